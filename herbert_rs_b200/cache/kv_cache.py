@@ -21,7 +21,7 @@ contiguous, so the query heads of a group read each key tile once.
 
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -47,8 +47,23 @@ class StateNeed:
 
 @dataclass(frozen=True)
 class CacheNeed:
+    """What one schedule step keeps per sequence: paged keys/values, one fixed-size state, and any
+    number of further fixed-size states by name (a layer whose input convolution, mixer and mixer's
+    own convolutions each carry something from token to token): `states` is a tuple of
+    (name, StateNeed)."""
+
     kv: Optional[KVNeed] = None
     state: Optional[StateNeed] = None
+    states: tuple = ()
+
+    def merged(self, other: "CacheNeed", prefix: str = "") -> "CacheNeed":
+        """This need and another's side by side; the other's unnamed state and named states get `prefix`."""
+        if self.kv is not None and other.kv is not None:
+            raise CacheError("one schedule step can hold one key/value need")
+        more = tuple((prefix + n, s) for n, s in other.states)
+        if other.state is not None:
+            more = ((prefix + "state", other.state),) + more
+        return CacheNeed(self.kv if self.kv is not None else other.kv, self.state, self.states + more)
 
 
 @dataclass
@@ -61,6 +76,13 @@ class CacheView:
     writes_kv: bool = True              # False: this step reads what another step stored
     state: Optional[torch.Tensor] = None  # [slots, *shape]
     page_size: int = 0
+    states: dict = field(default_factory=dict)   # name -> [slots, *shape], the step's named states
+
+    def sub(self, prefix: str) -> "CacheView":
+        """The view a part of a composite mixer sees: the named states under `prefix` with the prefix
+        taken off ("<prefix>state" becomes its unnamed state), and the step's keys and values."""
+        inner = {n[len(prefix):]: t for n, t in self.states.items() if n.startswith(prefix)}
+        return CacheView(self.kv_group, self.k, self.v, self.writes_kv, inner.pop("state", None), self.page_size, inner)
 
 
 class SequenceCache:
@@ -87,6 +109,7 @@ class SequenceCache:
         self._state_entries: List[List[int]] = []
         self.step_kv: List[Optional[tuple]] = []      # per step: (group, entry, writes)
         self.step_state: List[Optional[tuple]] = []   # per step: (group, entry)
+        self.step_states: List[dict] = []             # per step: name -> (group, entry), the named states
         for i, need in enumerate(needs):
             src = reads_cache_of[i]
             if src is not None:
@@ -108,14 +131,15 @@ class SequenceCache:
             else:
                 self.step_kv.append(None)
             if need.state is not None:
-                if need.state not in self.state_needs:
-                    self.state_needs.append(need.state)
-                    self._state_entries.append([])
-                g = self.state_needs.index(need.state)
-                self._state_entries[g].append(i)
-                self.step_state.append((g, len(self._state_entries[g]) - 1))
+                self.step_state.append(self._state_entry(need.state, i))
             else:
                 self.step_state.append(None)
+            named = {}
+            for name, sn in need.states:
+                if name in named:
+                    raise CacheError(f"schedule step {i} names the state {name!r} twice")
+                named[name] = self._state_entry(sn, i)
+            self.step_states.append(named)
 
         self.slots = IdPool(num_slots, "slot")
         self.pools = [IdPool(num_pages, f"page of group {g}") for g in range(len(self.kv_needs))]
@@ -133,6 +157,15 @@ class SequenceCache:
             for g, need in enumerate(self.state_needs):
                 self.state.append(torch.zeros((len(self._state_entries[g]), num_slots, *need.shape),
                                               dtype=need.dtype, device=device))
+
+    def _state_entry(self, need: StateNeed, step: int) -> tuple:
+        """(group, entry) of one more state of this shape and dtype, owned by schedule step `step`."""
+        if need not in self.state_needs:
+            self.state_needs.append(need)
+            self._state_entries.append([])
+        g = self.state_needs.index(need)
+        self._state_entries[g].append(step)
+        return g, len(self._state_entries[g]) - 1
 
     # -- sizes -----------------------------------------------------------------------------
     @property
@@ -272,6 +305,8 @@ class SequenceCache:
         if st is not None and self.state:
             g, e = st
             v.state = self.state[g][e]
+        if self.state:
+            v.states = {name: self.state[g][e] for name, (g, e) in self.step_states[step].items()}
         return v
 
     def check(self) -> None:

@@ -28,6 +28,9 @@ class NormSpec:
     kind: str = "rmsnorm"
     weight_name: str = "weight"     # the weight's tensor name under the part's prefix
     weight_offset: float = 0.0
+    # rmsnorm only: the axis is cut into this many equal consecutive parts and each part is divided by
+    # its own root mean square; the weight still spans the whole axis
+    groups: int = 1
 
 
 @dataclass(frozen=True)
@@ -57,6 +60,19 @@ class ScaledRotarySpec:
     fast: float = 0.0
     slow: float = 0.0
     kind: str = "scaled_rope"
+
+
+@dataclass(frozen=True)
+class RotaryPairsSpec:
+    """Rotary pairs whose angles are computed from the position (no table): pair m of `rotary_dim`
+    channels turns by p * theta^(-2m/rotary_dim) / linear_factor.  layout "interleaved": pair m is
+    channels (2m, 2m + 1); "halves": (m, m + rotary_dim/2).  Channels beyond rotary_dim pass unchanged."""
+
+    rotary_dim: int
+    theta: float
+    linear_factor: float = 1.0
+    layout: str = "interleaved"
+    kind: str = "rope_pairs"
 
 
 @dataclass(frozen=True)
@@ -130,18 +146,92 @@ class AttentionSpec:
     softcap: Optional[float] = None
     sink: bool = False
     names: tuple = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "sink")
+    # A third form, taken when `position` is a RotaryPairsSpec or any of the following is set:
+    # `value_dim`: the values' size per head where it differs from `head_dim` (the queries' and keys');
+    # `whole_qk_norm`: one RMS norm over the whole q projection and one over the whole k projection
+    #     (all heads at once, weights named by `norm_names`, eps of `qk_norm`), before the rotation;
+    # `value_rotation`: the value at position j is stored turned by j (over all of its channels), and
+    #     a head's result at position i is turned back by -i: the result then depends on i - j only.
+    value_dim: Optional[int] = None
+    whole_qk_norm: bool = False
+    value_rotation: Optional[RotaryPairsSpec] = None
+    norm_names: tuple = ("q_norm.weight", "k_norm.weight")
+
+
+@dataclass(frozen=True)
+class LightningAttentionSpec:
+    """Linear attention with a matrix of state per head and one constant decay per head:
+    q, k, v = silu(W h);  S_t = decay_h S_{t-1} + k_t v_t^T;  o_t = S_t^T q_t;  the heads' results,
+    side by side, pass one RMS norm (weight over all of them), are multiplied by sigmoid(G h) and
+    projected."""
+
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    decay: tuple
+    norm_eps: float
+    kind: str = "lightning"
+    names: tuple = ("q", "k", "v", "g", "o", "norm")
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """The gated delta rule: per head S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with
+    q, k of `qk_heads` heads (value head h uses q/k head h / (num_heads / qk_heads)), each of q, k, v
+    through a short causal convolution of `conv_taps` taps and silu, q and k made unit vectors per
+    head (q also times key_dim^-1/2), beta = sigmoid(B h), g = exp(-exp(A_log) softplus(A h + dt_bias));
+    per-head RMS norm of o (weight of value_dim, shared), gate silu(G h), output product."""
+
+    hidden_size: int
+    num_heads: int
+    qk_heads: int
+    key_dim: int
+    value_dim: int
+    conv_taps: int
+    norm_eps: float
+    kind: str = "gated_delta"
+    unit_eps: float = 1e-6      # inside the root of the unit vectors' length
+
+
+@dataclass(frozen=True)
+class SideBySideSpec:
+    """Two mixers that read the same input; the result is left_scale * left + right_scale * right.
+    Their tensors lie under the sub-prefixes of `names`."""
+
+    left: object
+    right: object
+    left_scale: float
+    right_scale: float
+    kind: str = "side_by_side"
+    names: tuple = ("left", "right")
+
+
+@dataclass(frozen=True)
+class PairEmbeddingSpec:
+    """A second embedding table chosen by a token and its predecessor: row
+    (previous * mul_prev + token * mul_cur) mod buckets of a table of buckets + 1 rows, whose last
+    row serves a sequence's first token; it is added to the token's own embedding."""
+
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    table_name: str = "bigram"
 
 
 @dataclass(frozen=True)
 class SwiGLUSpec:
-    """Dense gated feed-forward: down(act(gate(x)) * up(x)); act "silu", "gelu_tanh" or "gelu".
-    `names`: the tensors of gate, up and down."""
+    """Dense gated feed-forward: down(act(gate(x)) * up(x)); act "silu", "gelu_tanh", "gelu" or "relu".
+    `names`: the tensors of gate, up and down; with `bias` every projection adds a vector named as
+    its matrix with `bias_suffix`."""
 
     hidden_size: int
     intermediate_size: int
     kind: str = "swiglu"
     activation: str = "silu"
     names: tuple = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+    bias: bool = False
+    bias_suffix: str = ".b"
 
 
 @dataclass(frozen=True)
@@ -183,7 +273,9 @@ class BlockSpec:
     kind "prenorm": h = x + mixer(norm1(x)); out = h + ffn(norm2(h)).
     kind "sublayer_norm": h = x + s1 * norm1(mixer(x)); out = h + s2 * norm2(ffn(h)): the sublayers
     read the stream itself and their results are normed; s1, s2 are per-channel scales named by
-    `layer_scale` (None: no scales); `ffn` may be None (then the layer ends after the mixer).
+    `layer_scale` (None: no scales); `ffn` may be None (then the layer ends after the mixer).  With
+    `input_conv_taps` the mixer reads x + conv(x) instead, a causal convolution over time on each
+    channel (tensor `input_conv_name`, [width, taps], the last column weighs the token itself).
     kind "parallel": h = norm1(x); out = x + residual_mult * (mixer(h) + ffn(h)): one norm, both
     sublayers read its result; `ffn` may be None; norm2 is unused (None).
     `names` maps the block's local part names to the sub-prefixes used in tensor names.
@@ -196,6 +288,8 @@ class BlockSpec:
     kind: str = "prenorm"
     layer_scale: Optional[tuple] = None
     residual_mult: float = 1.0
+    input_conv_taps: Optional[int] = None
+    input_conv_name: str = "canon1"
     names: tuple = (
         ("norm1", "input_layernorm"),
         ("mixer", "self_attn"),
@@ -243,6 +337,10 @@ class ModelSpec:
     # A learned vector per position, [max_position, hidden], added (unscaled) to the embedding row;
     # None: the model has none.  A sequence cannot grow beyond the table.
     position_table_name: Optional[str] = None
+    # A table chosen by (previous token, token), added to the embedding; the previous token is state.
+    pair_embedding: Optional[PairEmbeddingSpec] = None
+    # c: logits <- c * tanh(logits / c)
+    logit_softcap: Optional[float] = None
     extra: dict = field(default_factory=dict)     # free for an architecture's own model class
 
 

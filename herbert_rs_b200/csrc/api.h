@@ -22,6 +22,7 @@ extern "C" {
 #define HB_ACT_SILU 0       // z / (1 + exp(-z))
 #define HB_ACT_GELU_TANH 1  // 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
 #define HB_ACT_GELU 2       // 0.5 z (1 + erf(z / sqrt(2)))
+#define HB_ACT_RELU 3       // max(z, 0)
 
 
 // attention_decode.cu: decode attention over the paged cache (one query per sequence, keys cut into splits)
@@ -181,6 +182,43 @@ int hb_argmax(const float* logits, int ld, int n_rows, int vocab, int* out, void
     scratch_words, void* stream);
 int hb_sample(const float* logits, int ld, int n_rows, int vocab, float temperature, int top_k, float top_p,
     const float* uniforms, int* out, int* overflow, void* stream);
+
+// group_norm.cu: RMS norm in groups (alone, or of a sublayer's result on its way into the stream), a gated activation with biases, a weighted sum of two arrays, a tanh cap
+int hb_group_rmsnorm(int dtype, const float* x, const float* w, void* out, const int* rows, int n_rows, int dim,
+    int groups, float eps, void* stream);
+int hb_group_rmsnorm_residual(int dtype, const float* y, int ldy, const float* bias, const float* w, float* x,
+    void* h, int n_rows, int dim, int groups, float eps, void* stream);
+int hb_axpby(float* y, int ldy, float a, const float* z, int ldz, float b, int rows, int cols, void* stream);
+int hb_bias_glu(int dtype, const float* gu, int ld, const float* bias, void* out, int ldo, int n_tokens, int
+    inter, int interleave, int act, void* stream);
+int hb_tanh_cap(float* x, int ld, float cap, int rows, int cols, void* stream);
+
+// short_conv.cu: a short causal convolution over time whose last inputs are state; an embedding plus a row chosen by (previous token, token)
+int hb_short_conv(int out_dtype, const float* in, int ld_in, const float* w, float* state, const int* seq_slot,
+    const int* seq_start, const int* seq_pos0, void* out, int ldo, int n_seqs, int max_q_len, int channels, int
+    taps, int add_input, int act_silu, void* stream);
+int hb_pair_embed(int dtype, const void* table, const void* pair_table, const int* ids, const int* tok_seq,
+    const int* tok_pos, const int* seq_slot, const int* seq_start, int* last_id, float* out, int n_tokens, int
+    hidden, int vocab, int buckets, long long mul_prev, long long mul_cur, float scale, void* stream);
+
+// linear_scan.cu: recurrent mixers with a matrix of state per head: the decaying form and the gated delta rule
+int hb_silu_columns(float* x, int ld, int col0, int cols, int rows, void* stream);
+int hb_delta_prepare(float* qk, int ld, int q_off, int k_off, int qk_heads, int dk, float qscale, const float*
+    ab, int ldab, int b_off, int a_off, const float* a_log, const float* dt_bias, float* gates, int heads, int
+    n_tokens, void* stream);
+int hb_linear_scan(int delta, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const
+    float* gates, const float* decay, float* state, const int* seq_slot, const int* seq_start, float* out, int ldo,
+    int n_seqs, int heads, int qk_heads, int dk, int dv, void* stream);
+int hb_gated_rmsnorm(int dtype, const float* o, int ldo, const float* w, float eps, const float* gate, int ldg,
+    void* y, int ldy, int n_tokens, int units, int n, int act, void* stream);
+
+// rotary_pairs.cu: whole-projection q/k norm, rotation of pairs by position (q, k and v), cache write; the turn back of the results
+int hb_qkv_rotary_cache(int dtype, const float* rows, int ld, const float* wq, const float* wk, float eps, int
+    whole_norm, const float* fqk, int rot, int halves, const float* fv, const int* tok_seq, const int* tok_pos,
+    const int* seq_pages, int pages_stride, void* q_out, int ldq, void* kcache, void* vcache, int n_tokens, int nh,
+    int nkv, int dk, int dv, int hd, int page_size, int write_cache, void* stream);
+int hb_rotate_heads_back(int dtype, const void* att, int ld, int hd, const float* fv, int halves, const int*
+    tok_pos, void* y, int ldy, int n_tokens, int nh, int dv, void* stream);
 
 #ifdef __cplusplus
 }

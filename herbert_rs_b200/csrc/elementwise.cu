@@ -147,7 +147,7 @@ extern "C" int hb_rmsnorm(int dtype, const float* x, const float* w, void* out, 
 // ---------------------------------------------------------------------------------------------
 // gu: [n_tokens, 2*inter] with leading dimension ld.  interleave == 0: gate columns [0, inter),
 // up columns [inter, 2*inter).  interleave == 8: blocks of 16 columns, 8 gate then 8 up.
-// out = act(gate) * up; act: silu, or gelu in its tanh or erf form (HB_ACT_*).
+// out = act(gate) * up; act: silu, gelu in its tanh or erf form, or relu (HB_ACT_*).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out, int ldo,
                               int inter, int interleave, int act) {
@@ -168,6 +168,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, int ld, T* __restrict__ 
   const float g = to_f32(row[gi]), u = to_f32(row[ui]);
   const float a = (act == HB_ACT_GELU_TANH ? 0.5f * g * (1.0f + tanhf(0.79788456080286535588f * (g + 0.044715f * g * g * g)))
                    : act == HB_ACT_GELU    ? 0.5f * g * (1.0f + erff(g * 0.70710678118654752440f))
+                   : act == HB_ACT_RELU    ? fmaxf(g, 0.0f)
                                            : g / (1.0f + expf(-g))) * u;
   out[(size_t)t * ldo + i] = from_f32<T>(a);
 }
@@ -177,6 +178,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, int ld, T* __restrict__ 
 __device__ __forceinline__ float glu_act(float g, int act) {
   return act == HB_ACT_GELU_TANH ? 0.5f * g * (1.0f + tanhf(0.79788456080286535588f * (g + 0.044715f * g * g * g)))
          : act == HB_ACT_GELU    ? 0.5f * g * (1.0f + erff(g * 0.70710678118654752440f))
+         : act == HB_ACT_RELU    ? fmaxf(g, 0.0f)
                                  : g / (1.0f + expf(-g));
 }
 __global__ void swiglu8_bf16_kernel(const bf16* __restrict__ gu, int ld, bf16* __restrict__ out, int ldo, int groups, int act) {

@@ -1,5 +1,6 @@
 """Models: the generic decoder, and the architectures registered for it."""
 
+from ..config.begupel import BegupelConfig
 from ..config.kebisun import KebisunConfig
 from ..config.qwen3 import Qwen3Config
 from ..config.votapel import VotapelConfig
@@ -14,5 +15,9 @@ register_architecture("Kebisun", KebisunConfig)
 # Parallel blocks (one norm, attention and a routed feed-forward side by side) of attention whose values
 # are its keys, with biases, a query temperature, capped scores and a sink; learned position vectors.
 register_architecture("Votapel", VotapelConfig)
+# Layers of lightning attention (a decaying matrix state per head) and of windowed attention with rotated
+# values beside a gated delta rule; an input convolution per layer, RMS norms in groups on the sublayers'
+# results, a pair embedding, capped logits.
+register_architecture("Begupel", BegupelConfig)
 
 __all__ = ["DecoderModel"]

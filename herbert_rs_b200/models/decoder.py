@@ -9,6 +9,10 @@ on exactly the rows whose logits are asked for, gathered before the norm.
 The order in which blocks run is the spec's `schedule`, a list: a block may be named twice (its
 weights run twice, each run with its own cache entry) and a step may read the cache entry of an
 earlier step instead of storing its own.
+
+Options of the spec: a scaled embedding, a learned vector per position, a second table chosen by (previous
+token, token) whose previous token is kept per sequence in the cache's fixed-size region (the first schedule
+step's entry carries it under the name "embedding.last_id"), a tanh cap on the logits.
 """
 
 from __future__ import annotations
@@ -20,12 +24,14 @@ import torch
 from .. import ops
 from ..config.specs import ModelSpec
 from ..errors import ConfigError
+from ..cache import CacheNeed, StateNeed
 from ..parts.base import ParamSpec
 from ..registry import build_part
 
 
 # A spec whose positions have no bound of their own says so with this number (or more).
 NO_POSITION_LIMIT = 1 << 30
+_LAST_ID = "embedding.last_id"
 
 
 class DecoderModel:
@@ -36,6 +42,7 @@ class DecoderModel:
         self.embed = None
         self.head = None
         self.position_table = None      # [max_position, hidden] learned vectors, if the spec names one
+        self.pair_table = None          # [buckets + 1, hidden], if the spec has a pair embedding
         for i, st in enumerate(spec.schedule):
             if not (0 <= st.layer < len(self.blocks)):
                 raise ConfigError(f"schedule step {i} names layer {st.layer}, but there are {len(self.blocks)} layers")
@@ -51,6 +58,8 @@ class DecoderModel:
             # a configuration that does not say how many positions the table has leaves it to the stored tensor
             rows = s.max_position if s.max_position < NO_POSITION_LIMIT else -1
             out[s.position_table_name] = ParamSpec((rows, s.hidden_size), free_size=4096)
+        if s.pair_embedding is not None:
+            out[s.pair_embedding.table_name] = ParamSpec((s.pair_embedding.buckets + 1, s.hidden_size))
         for i, b in enumerate(self.blocks):
             for name, ps in b.param_specs().items():
                 out[self.block_prefix(i) + name] = ps
@@ -75,6 +84,9 @@ class DecoderModel:
 
     def load_position_table(self, t: torch.Tensor) -> None:
         self.position_table = t.contiguous()
+
+    def load_pair_table(self, t: torch.Tensor) -> None:
+        self.pair_table = t.contiguous()
 
     def longest_sequence(self) -> int:
         """The longest sequence the model can place: the spec's limit, and the position table's rows."""
@@ -101,7 +113,11 @@ class DecoderModel:
 
     # -- cache -----------------------------------------------------------------------------
     def cache_needs(self) -> List:
-        return [self.blocks[st.layer].cache_need() for st in self.spec.schedule]
+        needs = [self.blocks[st.layer].cache_need() for st in self.spec.schedule]
+        if self.spec.pair_embedding is not None:
+            last = CacheNeed(states=((_LAST_ID, StateNeed((1,), torch.int32)),))
+            needs[0] = needs[0].merged(last)
+        return needs
 
     def reads_cache_of(self) -> List:
         return [st.reads_cache_of for st in self.spec.schedule]
@@ -114,7 +130,12 @@ class DecoderModel:
         ws = self.rt.workspace
         ws.rewind()
         x = ws.take((batch.n_tokens, self.spec.hidden_size), torch.float32)
-        ops.embed(self.embed, batch.token_ids, x, self.spec.embedding_scale, self.position_table, batch.tok_pos)
+        pe = self.spec.pair_embedding
+        if pe is not None:
+            ops.pair_embed(self.embed, self.pair_table, batch, cache.view(0).states[_LAST_ID], x, pe.buckets, pe.mul_prev,
+                           pe.mul_cur, self.spec.embedding_scale)
+        else:
+            ops.embed(self.embed, batch.token_ids, x, self.spec.embedding_scale, self.position_table, batch.tok_pos)
         # a block may begin the first norm of the block that runs after it (parts/base.py)
         sched, pending = self.spec.schedule, None
         for i, st in enumerate(sched):
@@ -135,4 +156,6 @@ class DecoderModel:
         self.final_norm.forward(x, hn, rows=batch.want_rows)
         logits = ws.take((batch.n_want, self.spec.vocab_size), torch.float32)
         ops.gemm(hn, self.head, logits, ops.EPI_STORE_F32)
+        if self.spec.logit_softcap:
+            ops.tanh_cap(logits, self.spec.logit_softcap)
         return logits

@@ -18,8 +18,8 @@ from . import lib as _libmod
 from .options import KernelOptions
 
 F32, BF16 = 0, 1
-ACT_SILU, ACT_GELU_TANH, ACT_GELU = 0, 1, 2
-ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "gelu": ACT_GELU}
+ACT_SILU, ACT_GELU_TANH, ACT_GELU, ACT_RELU = 0, 1, 2, 3
+ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "gelu": ACT_GELU, "relu": ACT_RELU}
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
 SKINNY_MAX_ROWS = 64
 # The one place where a choice between kernels can be changed (by a measurement script or a test
@@ -98,6 +98,28 @@ _SIGS = {
                      c_int, c_int, c_float, c_void_p],
     "hb_moe_experts": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                        c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_group_rmsnorm": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+    "hb_group_rmsnorm_residual": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                                  c_void_p],
+    "hb_axpby": [c_void_p, c_int, c_float, c_void_p, c_int, c_float, c_int, c_int, c_void_p],
+    "hb_bias_glu": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_tanh_cap": [c_void_p, c_int, c_float, c_int, c_int, c_void_p],
+    "hb_short_conv": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                      c_int, c_int, c_int, c_int, c_void_p],
+    "hb_pair_embed": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                      c_int, c_int, c_int, ctypes.c_longlong, ctypes.c_longlong, c_float, c_void_p],
+    "hb_silu_columns": [c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_delta_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p,
+                         c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "hb_linear_scan": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_gated_rmsnorm": [c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                         c_int, c_void_p],
+    "hb_qkv_rotary_cache": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_void_p, c_int, c_int, c_void_p,
+                            c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                            c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_rotate_heads_back": [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                             c_void_p],
 }
 _fns: dict = {}
 
@@ -456,6 +478,162 @@ def gla_output(o, w, eps, gate, out, heads, dv) -> None:
     _check(o, torch.float32, "o"); _check(w, torch.float32, "w"); _check(gate, torch.float32, "gate"); _check(out, None, "out")
     _run("hb_gla_output", dtype_code(out.dtype), o.data_ptr(), o.stride(0), w.data_ptr(), float(eps), gate.data_ptr(),
          gate.stride(0), out.data_ptr(), out.stride(0), o.shape[0], int(heads), int(dv), _stream())
+
+
+def group_rmsnorm(x, w, out, eps, groups=1, rows=None) -> None:
+    """out[r] = row rows[r] (or r) of x, cut into `groups` equal consecutive parts, each divided by its own
+    sqrt(mean(part^2) + eps), the whole times w; x and w float, out in its own dtype."""
+    _check(x, torch.float32, "x"); _check(w, torch.float32, "w"); _check(out, None, "out")
+    if not (x.is_contiguous() and out.is_contiguous()):
+        raise BackendError("group_rmsnorm: x and out must be contiguous")
+    _run("hb_group_rmsnorm", dtype_code(out.dtype), x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(rows), out.shape[0],
+         x.shape[-1], int(groups), float(eps), _stream())
+
+
+def group_rmsnorm_residual(y, w, x, h, eps, groups, dtype, bias=None) -> None:
+    """x += GN(y + bias) * w with GN the RMS norm in `groups` parts (bias [D] float or None); h, if given,
+    receives the updated x in the activation dtype `dtype`."""
+    _check(y, torch.float32, "y"); _check(w, torch.float32, "w"); _check(x, torch.float32, "x")
+    if h is not None:
+        _check(h, dtype, "h")
+    if bias is not None:
+        _check(bias, torch.float32, "bias")
+    if not x.is_contiguous() or (h is not None and not h.is_contiguous()):
+        raise BackendError("group_rmsnorm_residual: x and h must be contiguous")
+    _run("hb_group_rmsnorm_residual", dtype_code(dtype), y.data_ptr(), y.stride(0), _ptr(bias), w.data_ptr(), x.data_ptr(),
+         _ptr(h), x.shape[0], x.shape[1], int(groups), float(eps), _stream())
+
+
+def axpby(y, a, z, b) -> None:
+    """y = a * y + b * z, float arrays of one shape (rows may be strided)."""
+    _check(y, torch.float32, "y"); _check(z, torch.float32, "z")
+    if y.shape != z.shape:
+        raise BackendError("axpby: y and z must have one shape")
+    _run("hb_axpby", y.data_ptr(), y.stride(0), float(a), z.data_ptr(), z.stride(0), float(b), y.shape[0], y.shape[1], _stream())
+
+
+def add_row_bias(y, bias) -> None:
+    """y[r, :] += bias for every row (float)."""
+    _check(y, torch.float32, "y"); _check(bias, torch.float32, "bias")
+    if bias.numel() != y.shape[1]:
+        raise BackendError("add_row_bias: the bias must have one number per column")
+    _run("hb_axpby", y.data_ptr(), y.stride(0), 1.0, bias.data_ptr(), 0, 1.0, y.shape[0], y.shape[1], _stream())
+
+
+def bias_glu(gu, bias, out, interleave, act) -> None:
+    """out = act(gate + b) * (up + b) from float sums gu [T, 2 inter] (bias in gu's column layout, or None)."""
+    _check(gu, torch.float32, "gu"); _check(out, None, "out")
+    if bias is not None:
+        _check(bias, torch.float32, "bias")
+    _run("hb_bias_glu", dtype_code(out.dtype), gu.data_ptr(), gu.stride(0), _ptr(bias), out.data_ptr(), out.stride(0),
+         gu.shape[0], out.shape[1], int(interleave), int(act), _stream())
+
+
+def tanh_cap(x, cap) -> None:
+    """x <- cap * tanh(x / cap), float, in place."""
+    _check(x, torch.float32, "x")
+    _run("hb_tanh_cap", x.data_ptr(), x.stride(0), float(cap), x.shape[0], x.shape[1], _stream())
+
+
+def short_conv(inp, w, state, batch, out, add_input=False, silu=False) -> None:
+    """A causal convolution over time per channel: out_t = (in_t +) sum_j w[:, j] in_{t - taps + 1 + j} (then silu);
+    inp float [T, C] (rows may be strided), w float [C, taps], state float [slots, taps - 1, C] (the sequence's
+    last inputs: read for a step's first tokens, then replaced by the step's last inputs), out [T, C] in its dtype."""
+    _check(inp, torch.float32, "inp"); _check(w, torch.float32, "w"); _check(out, None, "out")
+    taps = w.shape[1]
+    if state is not None:
+        _check(state, torch.float32, "state")
+        if not state.is_contiguous() or tuple(state.shape[1:]) != (taps - 1, inp.shape[1]):
+            raise BackendError(f"short_conv: state of shape {tuple(state.shape)} does not hold {taps - 1} inputs of {inp.shape[1]} channels")
+    if not w.is_contiguous():
+        raise BackendError("short_conv: w must be contiguous")
+    _run("hb_short_conv", dtype_code(out.dtype), inp.data_ptr(), inp.stride(0), w.data_ptr(), _ptr(state),
+         batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(), batch.seq_pos0.data_ptr(), out.data_ptr(), out.stride(0),
+         batch.n_seqs, batch.max_q_len, inp.shape[1], taps, 1 if add_input else 0, 1 if silu else 0, _stream())
+
+
+def pair_embed(table, pair_table, batch, last_id, out, buckets, mul_prev, mul_cur, scale=1.0) -> None:
+    """out[t] = table[id_t] * scale + pair_table[(id_{t-1} * mul_prev + id_t * mul_cur) mod buckets] (row `buckets`
+    for a sequence's first token); the id before a step's first token is last_id[slot] (int32 [slots, 1]), where
+    the step then leaves its own last id."""
+    _check(table, None, "table"); _check(pair_table, table.dtype, "pair_table"); _check(out, torch.float32, "out")
+    _check(last_id, torch.int32, "last_id")
+    if pair_table.shape != (buckets + 1, table.shape[1]) or not pair_table.is_contiguous():
+        raise BackendError(f"pair_embed: the pair table must be [{buckets + 1}, {table.shape[1]}] and contiguous")
+    _run("hb_pair_embed", dtype_code(table.dtype), table.data_ptr(), pair_table.data_ptr(), batch.token_ids.data_ptr(),
+         batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(),
+         last_id.data_ptr(), out.data_ptr(), batch.n_tokens, table.shape[1], table.shape[0], int(buckets), int(mul_prev),
+         int(mul_cur), float(scale), _stream())
+
+
+def silu_columns(x, col0, cols) -> None:
+    """x[:, col0:col0 + cols] <- silu of it, float, in place."""
+    _check(x, torch.float32, "x")
+    _run("hb_silu_columns", x.data_ptr(), x.stride(0), int(col0), int(cols), x.shape[0], _stream())
+
+
+def delta_prepare(qk, q_off, k_off, qk_heads, dk, qscale, ab, b_off, a_off, a_log, dt_bias, gates, heads) -> None:
+    """In place on float rows qk: every q and k head (column ranges from q_off, k_off) becomes x / sqrt(sum x^2 + 1e-6),
+    q also times qscale.  gates [T, 2 heads] float: g = exp(-exp(a_log) softplus(ab[:, a_off + h] + dt_bias)), then
+    beta = sigmoid(ab[:, b_off + h])."""
+    for t, n in ((qk, "qk"), (ab, "ab"), (a_log, "a_log"), (dt_bias, "dt_bias"), (gates, "gates")):
+        _check(t, torch.float32, n)
+    if not gates.is_contiguous():
+        raise BackendError("delta_prepare: gates must be contiguous")
+    _run("hb_delta_prepare", qk.data_ptr(), qk.stride(0), int(q_off), int(k_off), int(qk_heads), int(dk), float(qscale),
+         ab.data_ptr(), ab.stride(0), int(b_off), int(a_off), a_log.data_ptr(), dt_bias.data_ptr(), gates.data_ptr(),
+         int(heads), qk.shape[0], _stream())
+
+
+def linear_scan(q, k, v, state, batch, out, heads, qk_heads, dk, dv, gates=None, decay=None) -> None:
+    """The recurrence of a matrix state per head over every sequence's tokens of the step, in order, from and into
+    state[slot] ([slots, heads, dk, dv] float).  With `gates` ([T, 2 heads]: g, beta) the gated delta rule
+    S <- g S; u = beta (v - S^T k); S <- S + k u^T; with `decay` ([heads]) S <- d S + k v^T.  o = S^T q.
+    q, k [T, qk_heads dk], v and out [T, heads dv]: float column ranges of rows."""
+    for t, n in ((q, "q"), (k, "k"), (v, "v"), (state, "state"), (out, "out")):
+        _check(t, torch.float32, n)
+    if not state.is_contiguous() or tuple(state.shape[1:]) != (heads, dk, dv):
+        raise BackendError(f"linear_scan: state of shape {tuple(state.shape)} is not [slots, {heads}, {dk}, {dv}]")
+    if (gates is None) == (decay is None):
+        raise BackendError("linear_scan: give the delta rule's gates or the constant decays")
+    _run("hb_linear_scan", 1 if gates is not None else 0, q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(),
+         v.stride(0), _ptr(gates), _ptr(decay), state.data_ptr(), batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(),
+         out.data_ptr(), out.stride(0), batch.n_seqs, int(heads), int(qk_heads), int(dk), int(dv), _stream())
+
+
+def gated_rmsnorm(o, w, eps, gate, out, units, n, sigmoid_gate=False) -> None:
+    """out[t, u, :] = o[t, u, :] / sqrt(mean(o[t, u, :]^2) + eps) * w * act(gate[t, u, :]) for `units` runs of n columns;
+    w [n] is shared by the units (units == 1: one norm over the whole row).  act: silu, or the sigmoid."""
+    _check(o, torch.float32, "o"); _check(w, torch.float32, "w"); _check(gate, torch.float32, "gate"); _check(out, None, "out")
+    if w.numel() != n:
+        raise BackendError(f"gated_rmsnorm: the weight has {w.numel()} numbers, a unit {n}")
+    _run("hb_gated_rmsnorm", dtype_code(out.dtype), o.data_ptr(), o.stride(0), w.data_ptr(), float(eps), gate.data_ptr(),
+         gate.stride(0), out.data_ptr(), out.stride(0), o.shape[0], int(units), int(n), 1 if sigmoid_gate else 0, _stream())
+
+
+def qkv_rotary_cache(rows, wq, wk, eps, fqk, rot, halves, fv, batch, seq_pages, q_out, k_cache, v_cache, num_heads,
+                     num_kv_heads, dk, dv, hd, page_size, write_cache=True) -> None:
+    """Float rows [q: heads x dk | k: kv heads x dk | v: kv heads x dv]: q and k normed over the whole projection
+    (weights wq, wk; None: no norm), pair m of their first `rot` channels turned by p * fqk[m], pair m of all value
+    channels by p * fv[m] (fv None: values as they are); q into q_out (heads of hd channels), k and v into the paged
+    cache (heads of hd channels, zeros beyond dk and dv)."""
+    _check(rows, torch.float32, "rows"); _check(q_out, k_cache.dtype, "q_out")
+    for t, n in ((wq, "wq"), (wk, "wk"), (fqk, "fqk"), (fv, "fv")):
+        if t is not None:
+            _check(t, torch.float32, n)
+    _run("hb_qkv_rotary_cache", dtype_code(q_out.dtype), rows.data_ptr(), rows.stride(0), _ptr(wq), _ptr(wk), float(eps),
+         1 if wq is not None else 0, _ptr(fqk), int(rot), 1 if halves else 0, _ptr(fv), batch.tok_seq.data_ptr(),
+         batch.tok_pos.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0), q_out.data_ptr(), q_out.stride(0),
+         k_cache.data_ptr(), v_cache.data_ptr(), rows.shape[0], int(num_heads), int(num_kv_heads), int(dk), int(dv), int(hd),
+         int(page_size), 1 if write_cache else 0, _stream())
+
+
+def rotate_heads_back(att, hd, fv, halves, tok_pos, out, num_heads, dv) -> None:
+    """out[t, h, :dv] = the first dv channels of head h of att (heads of hd channels), pair m turned by -p * fv[m]
+    (fv None: copied)."""
+    _check(att, out.dtype, "att")
+    _run("hb_rotate_heads_back", dtype_code(out.dtype), att.data_ptr(), att.stride(0), int(hd), _ptr(fv), 1 if halves else 0,
+         tok_pos.data_ptr(), out.data_ptr(), out.stride(0), att.shape[0], int(num_heads), int(dv), _stream())
 
 
 def moe_route(h, w_router, ids, weights, top, renorm=False, score=0, groups=1, keep=1, group_top=2, weight_scale=1.0) -> None:

@@ -16,6 +16,13 @@ grows with the position, a cap on the scores, a sink in the softmax's denominato
 any of these takes the second path below: the product leaves float rows, one kernel adds the
 biases, applies the temperature and writes q and the cache (each number rounded once), and the
 attention kernels take the cap and the sink as parameters.
+
+A third form (`AttentionSpec.whole_qk_norm`, `value_dim`, `value_rotation`, or a position part that turns
+pairs by angles taken from the position): q and k are normed over the whole projection, the first channels of
+every q and k head are turned at the token's position, and the values are stored turned by their own
+position over all their channels; a head's result is turned back by the query's position, so that it depends
+on the distance only.  Values may be narrower or wider than keys: the cache's heads have max(dk, dv)
+channels, the unused ones are zeros, and the attention kernels run unchanged over heads of that size.
 """
 
 from __future__ import annotations
@@ -41,6 +48,11 @@ class AttentionMixer(Mixer):
         self.shared_values = bool(spec.values_are_keys)
         # the plain form (no option set) keeps the path with the fused kernels of the dense decoder
         self.plain = not (spec.bias or spec.values_are_keys or spec.q_temperature or spec.softcap or spec.sink)
+        self.pairs = bool(spec.whole_qk_norm or spec.value_dim is not None or spec.value_rotation is not None
+                          or getattr(spec.position, "kind", None) == "rope_pairs")
+        if self.pairs:
+            self._init_pairs()
+            return
         if not self.plain and (spec.qk_norm is not None or spec.position is not None):
             raise ConfigError("attention with biases, shared values, a query temperature, a cap or a sink has no "
                               "head norm and no rotation here")
@@ -54,8 +66,77 @@ class AttentionMixer(Mixer):
     def _matrices(self):
         return [self.n_q, self.n_k] + ([] if self.shared_values else [self.n_v])
 
+    # -- the third form ------------------------------------------------------------------------
+    def _init_pairs(self):
+        s = self.spec
+        if not self.plain or s.qk_norm is not None and not s.whole_qk_norm:
+            raise ConfigError("attention with rotated pairs, a norm over the whole projection or rotated values has "
+                              "none of the other options (biases, shared values, temperature, cap, sink, head norm)")
+        if s.whole_qk_norm and s.qk_norm is None:
+            raise ConfigError("a norm over the whole q and k projections needs its eps (qk_norm)")
+        self.plain = False
+        self.dk = s.head_dim
+        self.dv = s.value_dim if s.value_dim is not None else s.head_dim
+        self.hd = max(self.dk, self.dv)              # the cache's and the attention kernels' head size
+        self.q_dim, self.kv_dim = self.nh * self.dk, self.nkv * self.dk
+        self.qkv_dim = self.q_dim + self.kv_dim + self.nkv * self.dv
+        self.value_position = build_part("position", s.value_rotation, rt=self.rt) if s.value_rotation is not None else None
+        if self.value_position is not None and self.value_position.rotary_dim != self.dv:
+            raise ConfigError(f"values of {self.dv} channels are turned over all of them, not {self.value_position.rotary_dim}")
+        if self.position is not None and self.value_position is not None and self.position.halves != self.value_position.halves:
+            raise ConfigError("keys and values are turned in one layout of pairs")
+        self.shares_norms = False
+        self.can_store = True
+        self.shared_values = False
+
+    def _param_specs_pairs(self):
+        s = self.spec
+        p = {
+            self.n_q: ParamSpec((self.q_dim, s.hidden_size)),
+            self.n_k: ParamSpec((self.kv_dim, s.hidden_size)),
+            self.n_v: ParamSpec((self.nkv * self.dv, s.hidden_size)),
+            self.n_o: ParamSpec((s.hidden_size, self.nh * self.dv)),
+        }
+        if s.whole_qk_norm:
+            p[s.norm_names[0]] = ParamSpec((self.q_dim,), role="vector", init="ones_noise")
+            p[s.norm_names[1]] = ParamSpec((self.kv_dim,), role="vector", init="ones_noise")
+        return p
+
+    def _load_pairs(self, tensors):
+        s = self.spec
+        self.wqkv = torch.cat([tensors[self.n_q], tensors[self.n_k], tensors[self.n_v]], dim=0).contiguous()
+        self.wo = tensors[self.n_o].contiguous()
+        if s.whole_qk_norm:
+            self.q_norm = tensors[s.norm_names[0]].contiguous()
+            self.k_norm = tensors[s.norm_names[1]].contiguous()
+
+    def _forward_pairs(self, h, residual, batch, cache, accumulate):
+        s, ws, T = self.spec, self.rt.workspace, h.shape[0]
+        rows = ws.take((T, self.qkv_dim), torch.float32)
+        ops.gemm(h, self.wqkv, rows, ops.EPI_STORE_F32, scratch=ws.take)
+        q = ws.take((T, self.nh * self.hd), h.dtype)
+        pages = batch.pages[cache.kv_group]
+        pos, vpos = self.position, self.value_position
+        halves = pos.halves if pos is not None else (vpos.halves if vpos is not None else False)
+        fv = vpos.freq if vpos is not None else None
+        ops.qkv_rotary_cache(rows, self.q_norm, self.k_norm, s.qk_norm.eps if s.qk_norm is not None else 0.0,
+                             pos.freq if pos is not None else None, pos.rotary_dim if pos is not None else 0, halves, fv,
+                             batch, pages, q, cache.k, cache.v, self.nh, self.nkv, self.dk, self.dv, self.hd,
+                             cache.page_size, write_cache=cache.writes_kv)
+        att = ws.take((T, self.nh * self.hd), h.dtype)
+        ops.attention(q, q.stride(0), att, cache.k, cache.v, batch, self.nh, self.nkv, self.hd, cache.page_size, s.scale,
+                      s.window, pages, scratch=ws.take)
+        if fv is not None or self.hd != self.dv:
+            y = ws.take((T, self.nh * self.dv), h.dtype)
+            ops.rotate_heads_back(att, self.hd, fv, halves, batch.tok_pos, y, self.nh, self.dv)
+        else:
+            y = att
+        ops.gemm(y, self.wo, residual, ops.EPI_RESIDUAL if accumulate else ops.EPI_STORE_F32, scratch=ws.take)
+
     def param_specs(self):
         s = self.spec
+        if self.pairs:
+            return self._param_specs_pairs()
         p = {
             self.n_q: ParamSpec((self.q_dim, s.hidden_size)),
             self.n_k: ParamSpec((self.kv_dim, s.hidden_size)),
@@ -75,6 +156,8 @@ class AttentionMixer(Mixer):
 
     def load(self, tensors):
         s = self.spec
+        if self.pairs:
+            return self._load_pairs(tensors)
         self.wqkv = torch.cat([tensors[n] for n in self._matrices()], dim=0).contiguous()
         self.wo = tensors[self.n_o].contiguous()
         if s.bias:
@@ -108,6 +191,8 @@ class AttentionMixer(Mixer):
         ops.gemm(att, self.wo, residual, ops.EPI_RESIDUAL if accumulate else ops.EPI_STORE_F32, scratch=ws.take)
 
     def forward(self, h, residual, batch, cache, next_norm=None, accumulate=True):
+        if self.pairs:
+            return self._forward_pairs(h, residual, batch, cache, accumulate)
         if not self.plain:
             return self._forward_options(h, residual, batch, cache, accumulate)
         ws, T = self.rt.workspace, h.shape[0]

@@ -6,6 +6,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from ..cache import CacheNeed, StateNeed
 from ..errors import ConfigError
 from ..registry import build_part, register_part
 from .base import Block, ParamSpec
@@ -81,9 +82,12 @@ class PreNormBlock(Block):
 class SublayerNormBlock(Block):
     """x += s1 * norm1(mixer(x)); x += s2 * norm2(ffn(x)): the sublayers read the residual stream
     itself (its rounding to the activation dtype on the bfloat16 path), their results are normed (a
-    layer norm) and multiplied channel by channel by a stored scale before they join the stream.
-    The spec may leave out the scales (`layer_scale` None) and the feed-forward (`ffn` None).  Norm,
-    scale and sum are one kernel, which also hands the next sublayer its input."""
+    layer norm, or an RMS norm in groups) and multiplied channel by channel by a stored scale before
+    they join the stream.  The spec may leave out the scales (`layer_scale` None) and the feed-forward
+    (`ffn` None).  Norm, scale and sum are one kernel, which also hands the next sublayer its input.
+    With `input_conv_taps` the mixer reads x + conv(x), a causal convolution over time on each channel
+    of the stream; the stream's rows of the last taps - 1 positions are kept per sequence in the cache's
+    fixed-size region (named "input_conv"), so a step continues where the one before ended."""
 
     def __init__(self, spec, rt):
         self.spec, self.rt = spec, rt
@@ -98,9 +102,14 @@ class SublayerNormBlock(Block):
             if part is not None and not part.can_store:
                 raise ConfigError(f"{type(part).__name__} cannot store its result apart from the residual stream, "
                                   "which a block that norms a sublayer's result needs")
-        for norm in (spec.norm1, spec.norm2):
-            if norm.kind != "layernorm":
-                raise ConfigError("the block that norms a sublayer's result applies a layer norm")
+        for norm in (spec.norm1, spec.norm2) if self.ffn is not None else (spec.norm1,):
+            if norm.kind not in ("layernorm", "rmsnorm"):
+                raise ConfigError("the block that norms a sublayer's result applies a layer norm or an RMS norm")
+            if norm.kind == "rmsnorm" and (self.scale_names or norm.weight_offset):
+                raise ConfigError("the RMS norm of a sublayer's result has no channel scales and no weight offset")
+        self.taps = int(spec.input_conv_taps) if spec.input_conv_taps else 0
+        self.conv_name = spec.input_conv_name
+        self.conv_w = None
 
     @property
     def graph_safe(self):
@@ -126,6 +135,8 @@ class SublayerNormBlock(Block):
             out[self.scale_names[0]] = ParamSpec((dim,), role="vector", init="ones_noise")
             if self.ffn is not None:
                 out[self.scale_names[1]] = ParamSpec((dim,), role="vector", init="ones_noise")
+        if self.taps:
+            out[self.conv_name] = ParamSpec((self.spec.norm1.dim, self.taps), role="vector", init="normal")
         return out
 
     def load(self, tensors):
@@ -135,17 +146,35 @@ class SublayerNormBlock(Block):
             self.scale1 = tensors[self.scale_names[0]].contiguous()
             if self.ffn is not None:
                 self.scale2 = tensors[self.scale_names[1]].contiguous()
+        if self.taps:
+            self.conv_w = tensors[self.conv_name].contiguous()
 
     def weight_bytes(self):
         return sum(p.weight_bytes() for _, p in self.children()) + (8 * self.spec.norm1.dim if self.scale_names else 0)
 
     def cache_need(self):
-        return self.mixer.cache_need()
+        need = self.mixer.cache_need()
+        if self.taps > 1:
+            conv = StateNeed((self.taps - 1, self.spec.norm1.dim), torch.float32)
+            need = CacheNeed(need.kv, need.state, need.states + (("input_conv", conv),))
+        return need
+
+    def _join(self, y, norm, scale, x, h, bias=None):
+        """x += norm(y + bias) (* scale); h, if given, receives the new x in the activation dtype."""
+        if norm.kind == "rmsnorm":
+            ops.group_rmsnorm_residual(y, norm.weight, x, h, norm.eps, norm.groups, self.rt.dtype, bias=bias)
+            return
+        if bias is not None:
+            ops.add_row_bias(y, bias)
+        ops.layernorm_residual(y, norm.weight, scale, x, h, norm.eps, self.rt.dtype)
 
     def forward(self, x, batch, cache, normed=None, next_norm=None):
         ws, dtype = self.rt.workspace, self.rt.dtype
         wide = dtype == torch.float32
-        if wide:
+        if self.taps:
+            h = ws.take(x.shape, dtype)
+            ops.short_conv(x, self.conv_w, cache.states.get("input_conv"), batch, h, add_input=True)
+        elif wide:
             h = x
         else:
             h = ws.take(x.shape, dtype)
@@ -153,10 +182,15 @@ class SublayerNormBlock(Block):
         y = ws.take(x.shape, torch.float32)
         self.mixer.forward(h, y, batch, cache, accumulate=False)
         h2 = None if (wide or self.ffn is None) else ws.take(x.shape, dtype)
-        ops.layernorm_residual(y, self.norm1.weight, self.scale1, x, h2, self.norm1.eps, dtype)
+        self._join(y, self.norm1, self.scale1, x, h2)
         if self.ffn is not None:
-            self.ffn.forward(x if wide else h2, y, batch, accumulate=False)
-            ops.layernorm_residual(y, self.norm2.weight, self.scale2, x, None, self.norm2.eps, dtype)
+            bias = None
+            if getattr(self.ffn, "take_output_bias", None) is not None and self.ffn.take_output_bias() is not None:
+                bias = self.ffn.take_output_bias()
+                self.ffn.forward(x if wide else h2, y, batch, accumulate=False, with_output_bias=False)
+            else:
+                self.ffn.forward(x if wide else h2, y, batch, accumulate=False)
+            self._join(y, self.norm2, self.scale2, x, None, bias=bias)
         return None
 
 

@@ -6,15 +6,21 @@ in float, when the tensor is loaded, so every kernel and the norm shared between
 from __future__ import annotations
 
 from .. import ops
+from ..errors import ConfigError
 from ..registry import register_part
 from .base import Norm, ParamSpec
 
 
 class RMSNorm(Norm):
+    kind = "rmsnorm"
+
     def __init__(self, spec, rt):
         self.dim, self.eps, self.rt = spec.dim, spec.eps, rt
         self.name = getattr(spec, "weight_name", "weight")
         self.offset = float(getattr(spec, "weight_offset", 0.0))
+        self.groups = int(getattr(spec, "groups", 1))
+        if self.groups < 1 or self.dim % self.groups:
+            raise ConfigError(f"a norm over {self.dim} channels cannot be cut into {self.groups} equal parts")
         self.weight = None
 
     def param_specs(self):
@@ -29,14 +35,19 @@ class RMSNorm(Norm):
         return self.dim * 4
 
     def forward(self, x, out, rows=None):
-        ops.rmsnorm(x, self.weight, out, self.eps, rows)
+        if self.groups > 1:
+            ops.group_rmsnorm(x, self.weight, out, self.eps, self.groups, rows)
+        else:
+            ops.rmsnorm(x, self.weight, out, self.eps, rows)
 
     def shareable(self):
-        return (self.weight, self.eps)
+        return (self.weight, self.eps) if self.groups == 1 else None
 
 
 class LayerNorm(RMSNorm):
     """y = (x - mean(x)) / sqrt(var(x) + eps) * w, no bias, in float (var: mean of squared deviations)."""
+
+    kind = "layernorm"
 
     def forward(self, x, out, rows=None):
         ops.layernorm(x, self.weight, out, self.eps, rows)

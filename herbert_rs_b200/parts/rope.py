@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import torch
 
+from ..errors import ConfigError
 from ..registry import register_part
 from .base import Part
 
@@ -71,3 +72,27 @@ class ScaledRotary(Part):
 
 register_part("position", "rope", RotaryEncoding)
 register_part("position", "scaled_rope", ScaledRotary)
+
+
+def pair_frequencies(rotary_dim: int, theta: float, linear_factor: float = 1.0) -> torch.Tensor:
+    """theta^(-2m / rotary_dim) / linear_factor for m < rotary_dim / 2, computed in float64, as float32."""
+    m = torch.arange(rotary_dim // 2, dtype=torch.float64)
+    f = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * m / rotary_dim) / float(linear_factor)
+    return f.to(torch.float32)
+
+
+class RotaryPairs(Part):
+    """Frequencies of a `RotaryPairsSpec` on the device; the kernels take the angle position * frequency in
+    float and the accurate sine and cosine, so no table bounds the position."""
+
+    def __init__(self, spec, rt):
+        if spec.rotary_dim % 2 or spec.rotary_dim < 0:
+            raise ConfigError(f"{spec.rotary_dim} rotated channels have no pairs")
+        if spec.layout not in ("interleaved", "halves"):
+            raise ConfigError(f"unknown layout of rotated pairs {spec.layout!r}: interleaved, halves")
+        self.rotary_dim = spec.rotary_dim
+        self.halves = spec.layout == "halves"
+        self.freq = pair_frequencies(spec.rotary_dim, spec.theta, spec.linear_factor).to(rt.device) if spec.rotary_dim else None
+
+
+register_part("position", "rope_pairs", RotaryPairs)
