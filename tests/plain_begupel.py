@@ -175,6 +175,40 @@ def rotated_value_attention(h, W, p, m, eps, store=_keep):
 
 
 # ---- the gated delta rule ("right") -------------------------------------------------------------
+def delta_recurrence(q, k, v, decay, beta, state=None):
+    """q, k [T, G, dk]; v [T, H, dv]; decay, beta [T, H].  Per head: S <- g S; u = beta (v - S^T k); S <- S + k u^T;
+    o = S^T q.  `state`, a list, receives the final matrices [H, dk, dv]."""
+    T, H, dv = v.shape
+    G, dk = q.shape[1], q.shape[2]
+    o = torch.zeros(T, H, dv, dtype=v.dtype)
+    for hd in range(H):
+        g = hd // (H // G)
+        S = torch.zeros(dk, dv, dtype=v.dtype)
+        for t in range(T):
+            S = decay[t, hd] * S
+            u = beta[t, hd] * (v[t, hd] - S.T @ k[t, g])
+            S = S + torch.outer(k[t, g], u)
+            o[t, hd] = S.T @ q[t, g]
+        if state is not None:
+            state.append(S)
+    return o
+
+
+def decay_recurrence(q, k, v, decay, state=None):
+    """q, k [T, H, dk]; v [T, H, dv]; decay [H].  Per head: S <- d S + k v^T; o = S^T q."""
+    T, H, dv = v.shape
+    dk = q.shape[2]
+    o = torch.zeros(T, H, dv, dtype=v.dtype)
+    for hd in range(H):
+        S = torch.zeros(dk, dv, dtype=v.dtype)
+        for t in range(T):
+            S = float(decay[hd]) * S + torch.outer(k[t, hd], v[t, hd])
+            o[t, hd] = S.T @ q[t, hd]
+        if state is not None:
+            state.append(S)
+    return o
+
+
 def gated_delta_rule(h, W, p, m, eps, store=_keep):
     T = h.shape[0]
     dt = h.dtype
@@ -187,15 +221,7 @@ def gated_delta_rule(h, W, p, m, eps, store=_keep):
     beta = sigmoid(h @ W[p + "b"].to(dt).T)                                        # [T, H]
     decay = torch.exp(-torch.exp(W[p + "A_log"].to(dt)) * softplus(h @ W[p + "a"].to(dt).T + W[p + "dt_bias"].to(dt)))
     gate = h @ W[p + "g"].to(dt).T
-    o = torch.zeros(T, H, dv, dtype=dt)
-    for hd in range(H):
-        g = hd // (H // G)
-        S = torch.zeros(dk, dv, dtype=dt)
-        for t in range(T):
-            S = decay[t, hd] * S
-            u = beta[t, hd] * (v[t, hd] - S.T @ k[t, g])
-            S = S + torch.outer(k[t, g], u)
-            o[t, hd] = S.T @ q[t, g]
+    o = delta_recurrence(q, k, v, decay, beta)
     o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps) * W[p + "norm"].to(dt)
     y = o.reshape(T, H * dv) * silu(gate)
     return store(y) @ W[p + "o"].to(dt).T
@@ -216,12 +242,7 @@ def lightning(h, W, p, m, eps, store=_keep):
     k = silu(h @ W[p + "k"].to(dt).T).reshape(T, H, dk)
     v = silu(h @ W[p + "v"].to(dt).T).reshape(T, H, dv)
     gate = sigmoid(h @ W[p + "g"].to(dt).T)
-    o = torch.zeros(T, H, dv, dtype=dt)
-    for hd in range(H):
-        S = torch.zeros(dk, dv, dtype=dt)
-        for t in range(T):
-            S = float(m["decay"][hd]) * S + torch.outer(k[t, hd], v[t, hd])
-            o[t, hd] = S.T @ q[t, hd]
+    o = decay_recurrence(q, k, v, m["decay"])
     y = rms_norm(o.reshape(T, H * dv), W[p + "norm"].to(dt), eps) * gate
     return store(y) @ W[p + "o"].to(dt).T
 
@@ -263,3 +284,21 @@ def load(folder: str):
     with open(f"{folder}/config.json") as f:
         cfg = json.load(f)
     return cfg, read_safetensors(f"{folder}/model.safetensors")
+
+
+class PlainBegupel:
+    """The plain model of a folder, or of a configuration and tensors given directly."""
+
+    def __init__(self, folder: str = None, config: dict = None, tensors: Dict[str, torch.Tensor] = None):
+        if folder is not None:
+            config, tensors = load(folder)
+        self.cfg = config
+        self.w = {k: (v.float() if v.is_floating_point() else v) for k, v in tensors.items()}
+
+    def logits(self, ids, dtype=torch.float64, store=_keep) -> torch.Tensor:
+        return forward(list(ids), self.w, self.cfg, dtype, store)
+
+    def layers(self, ids, dtype=torch.float64):
+        out = []
+        forward(list(ids), self.w, self.cfg, dtype, _keep, layers_out=out)
+        return out
