@@ -216,6 +216,41 @@ def _votapel_config(width, heads, kv_heads, dim, experts, top, groups, keep, exp
             "residual_mult": 0.5, "layers": [{"type": "attention", "mixer": mixer, "mlp": moe} for _ in range(layers)]}
 
 
+def _begupel_config(width, heads, kv_heads, dim, vdim, window, scan_heads, scan_qk_heads, scan_dk, scan_dv, ff, vocab,
+                    buckets=65536, taps=4, groups=4):
+    lightning = {"heads": scan_heads, "dim": scan_dk, "vdim": scan_dv,
+                 "decay": [round(1.0 - 2.0 ** -(5 + 3 * h / max(1, scan_heads - 1)), 6) for h in range(scan_heads)]}
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "mask": {"size": window},
+            "rot": {"base": 10000.0, "dims": dim // 2, "scaling": {"factor": 4.0}}}
+    right = {"heads": scan_heads, "kv_heads": scan_qk_heads, "dim": scan_dk, "vdim": scan_dv, "conv": taps}
+    side = {"left": left, "right": right, "left_scale": 0.5, "right_scale": 0.5}
+    dense = {"kind": "dense", "ff": ff}
+    layers = [{"type": "lightning", "mixer": lightning, "mlp": dense}, {"type": "parallel", "mixer": side, "mlp": dense},
+              {"type": "lightning", "mixer": lightning, "mlp": dense}, {"type": "parallel", "mixer": side, "mlp": dense}]
+    return {"architecture": "Begupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": groups},
+            "canon": {"taps": taps}, "logit_softcap": 30.0,
+            "embedding": {"bigram": {"buckets": buckets, "mul_prev": 1000003, "mul_cur": 31}}, "layers": layers}
+
+
+BEGUPEL_SIZES = {
+    # Begupel layer sizes (two lightning layers, two with windowed attention beside a gated delta rule); beside them
+    # Kebisun with recurrent heads of the same number and sizes (the closest design: a scan over a matrix state, a
+    # windowed attention, a norm on every sublayer's result) and the dense decoder of the same width, depth, heads,
+    # head size and feed-forward width
+    "1k": (dict(width=1024, heads=8, kv_heads=4, dim=128, vdim=128, window=4096, scan_heads=8, scan_qk_heads=4, scan_dk=128,
+                scan_dv=128, ff=3072, vocab=32000),
+           dict(width=1024, heads=8, dim=64, rot=32, vdim=64, kv_rank=256, q_rank=384, window=4096, gla_heads=8, gla_dk=128,
+                gla_dv=128, ff=3072, experts=16, top=2, expert_ff=768, vocab=32000),
+           dict(hidden_size=1024, num_hidden_layers=4, num_attention_heads=8, num_key_value_heads=4, head_dim=128,
+                intermediate_size=3072, vocab_size=32000, eos_token_id=31999)),
+    "2k": (dict(width=2048, heads=16, kv_heads=8, dim=128, vdim=128, window=4096, scan_heads=16, scan_qk_heads=8, scan_dk=128,
+                scan_dv=128, ff=8192, vocab=32000),
+           dict(width=2048, heads=16, dim=128, rot=64, vdim=128, kv_rank=512, q_rank=768, window=4096, gla_heads=16, gla_dk=128,
+                gla_dv=128, ff=8192, experts=32, top=4, expert_ff=1408, vocab=32000),
+           dict(hidden_size=2048, num_hidden_layers=4, num_attention_heads=16, num_key_value_heads=8, head_dim=128,
+                intermediate_size=8192, vocab_size=32000, eos_token_id=31999)),
+}
+
 VOTAPEL_SIZES = {
     # Votapel layer sizes, and the dense decoder of the same width, depth, heads and head size beside them; a token's
     # experts and the shared one together are as wide as the dense feed-forward
@@ -276,6 +311,28 @@ def _launcher_work(name, n, ctx):
             return n * 6.0 * T * top * F * D, n * (min(E, T * top) * 3 * F * D * es + T * D * (es + 4))
         if name == "hb_moe_route":
             return n * 2.0 * T * ctx["experts"] * D, n * (T * D * es + ctx["experts"] * D * es)
+    elif ctx["kind"] == "begupel":
+        H, KV, D = ctx["heads"], ctx["kv_heads"], ctx["width"]
+        hd = max(ctx["dim"], ctx["vdim"])
+        sh, sg, dk, dv = ctx["scan_heads"], ctx["scan_qk_heads"], ctx["scan_dk"], ctx["scan_dv"]
+        if name in ("hb_attention_prefill_tc_bf16", "hb_attention_prefill_bf16", "hb_attention_decode_bf16", "hb_attention_simt"):
+            return n * 4.0 * pairs * H * hd, n * (2 * B * L * KV * hd * es + 2 * T * H * hd * es)
+        if name == "hb_linear_scan":
+            # half of the launches decay and add an outer product (4 operations a state entry), half run the delta
+            # rule (7); every launch reads q, k, v and writes o as floats and reads and writes every sequence's state
+            half = n / 2.0
+            rows = T * sh * (2 * dk + 2 * dv) * 4 + T * (2 * sg * dk + 2 * sh * dv + 2 * sh) * 4
+            return half * (4.0 + 7.0) * T * sh * dk * dv, half * rows + n * 2 * B * sh * dk * dv * 4
+        if name == "hb_group_rmsnorm_residual":
+            return n * 6.0 * T * D, n * T * D * (4 + 4 + 4 + es)
+        if name == "hb_short_conv":       # the stream's rows (D channels, every layer) and the delta rule's q, k, v rows
+            per = n / 6.0
+            C = 2 * sg * dk + sh * dv
+            return n * 8.0 * T * D, per * (4 * T * D * (4 + es) + 2 * T * C * 8)
+        if name == "hb_qkv_rotary_cache":
+            return n * 6.0 * T * (H + 2 * KV) * hd, n * T * ((H + 2 * KV) * hd * (4 + es))
+        if name == "hb_gated_rmsnorm":
+            return n * 8.0 * T * sh * dv, n * T * sh * dv * (4 + 4 + es)
     else:
         H, KV, hd, D = ctx["heads"], ctx["kv_heads"], ctx["head_dim"], ctx["width"]
         if name in ("hb_attention_prefill_tc_bf16", "hb_attention_prefill_bf16", "hb_attention_decode_bf16",
@@ -353,9 +410,9 @@ def _design_point(hb, ops, torch, np, cfg, ctx, pk, prompt_len, batch, steps, wa
 
 
 def run_design(args) -> int:
-    """`--design kebisun|votapel`: prefill and decode of that design at layer sizes that resemble a real
-    model's, beside the dense decoder of equal width, depth and feed-forward width (random weights,
-    bfloat16, four layers each)."""
+    """`--design begupel|kebisun|votapel`: prefill and decode of that design at layer sizes that resemble a
+    real model's, beside the dense decoder of equal width, depth and feed-forward width (random weights,
+    bfloat16, four layers each); Begupel also beside Kebisun with recurrent heads of equal sizes."""
     import numpy as np
     import torch
 
@@ -366,9 +423,14 @@ def run_design(args) -> int:
     sampler, windows = ClockSampler(), []
     sampler.start()
     result = {}
-    table, make = (DESIGN_SIZES, _kebisun_config) if args.design == "kebisun" else (VOTAPEL_SIZES, _votapel_config)
+    table, make = {"kebisun": (DESIGN_SIZES, _kebisun_config), "votapel": (VOTAPEL_SIZES, _votapel_config),
+                   "begupel": (BEGUPEL_SIZES, _begupel_config)}[args.design]
     for size in (sorted(table) if args.design_size == "all" else [args.design_size]):
-        kb, dense = table[size]
+        closest = None
+        if args.design == "begupel":
+            kb, closest, dense = table[size]
+        else:
+            kb, dense = table[size]
         kcfg = make(**kb)
         qcfg = dict(QWEN3_8B)
         qcfg.update(dense)
@@ -379,6 +441,9 @@ def run_design(args) -> int:
             args.design: _design_point(hb, ops, torch, np, kcfg, kctx, pk, args.prompt_len, args.batch, args.steps, args.warmup, windows),
             "dense": _design_point(hb, ops, torch, np, qcfg, qctx, pk, args.prompt_len, args.batch, args.steps, args.warmup, windows),
         }
+        if closest is not None:
+            result[size]["kebisun"] = _design_point(hb, ops, torch, np, _kebisun_config(**closest), dict(closest, kind="kebisun"), pk,
+                                                    args.prompt_len, args.batch, args.steps, args.warmup, windows)
     sampler.stop()
     print(json.dumps({"metric": f"{args.design.capitalize()} and the dense decoder at equal sizes: prefill and decode tokens/s", "unit": "tokens/s",
                       "n_gpus": 1, "impl": "ours", "dtype": "bf16", "data": "synthetic", "steps": args.steps, "warmup": args.warmup,
@@ -408,7 +473,7 @@ def main() -> int:
     ap.add_argument("--pdl-graph", type=int, default=None, help="programmatic dependent launch inside recorded decode steps (0, 1, 2)")
     ap.add_argument("--workload", default=None, choices=["0.6b", "32b"],
                     help="run only this workload of the baseline and print its line")
-    ap.add_argument("--design", default=None, choices=["kebisun", "votapel"],
+    ap.add_argument("--design", default=None, choices=["begupel", "kebisun", "votapel"],
                     help="measure this design beside the dense decoder at equal sizes instead of the headline workload")
     ap.add_argument("--design-size", default="all", choices=["all"] + sorted(DESIGN_SIZES))
     args = ap.parse_args()
