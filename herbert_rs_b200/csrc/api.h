@@ -208,7 +208,7 @@ int hb_delta_prepare(float* qk, int ld, int q_off, int k_off, int qk_heads, int 
     n_tokens, void* stream);
 int hb_linear_scan(int delta, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const
     float* gates, const float* decay, float* state, const int* seq_slot, const int* seq_start, float* out, int ldo,
-    int n_seqs, int heads, int qk_heads, int dk, int dv, void* stream);
+    int n_seqs, int max_q_len, int heads, int qk_heads, int dk, int dv, void* stream);
 int hb_gated_rmsnorm(int dtype, const float* o, int ldo, const float* w, float eps, const float* gate, int ldg,
     void* y, int ldy, int n_tokens, int units, int n, int act, void* stream);
 

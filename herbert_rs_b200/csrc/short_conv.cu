@@ -14,21 +14,21 @@
 #include "common.cuh"
 
 #define SC_THREADS 128
-#define SC_TOKENS 64   // tokens per CTA; at least taps - 1, so that only a sequence's first CTA reads its state
+#define SC_TOKENS 64   // most tokens per CTA; a CTA takes at least taps - 1, so that only a sequence's first CTA reads its state
 
 template <typename TO>
 __global__ void __launch_bounds__(SC_THREADS)
 short_conv_kernel(const float* __restrict__ in, int ld_in, const float* __restrict__ w, float* __restrict__ state,
                   const int* __restrict__ seq_slot, const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
-                  TO* __restrict__ out, int ldo, int C, int taps, int add_input, int act_silu) {
+                  TO* __restrict__ out, int ldo, int C, int taps, int add_input, int act_silu, int span) {
   pdl_wait();
   pdl_launch();
   const int c = blockIdx.x * SC_THREADS + threadIdx.x;
   const int b = blockIdx.z;
   const int t0 = seq_start[b], n = seq_start[b + 1] - t0;
-  const int lo = blockIdx.y * SC_TOKENS;
+  const int lo = blockIdx.y * span;
   if (lo >= n || c >= C) return;
-  const int hi = lo + SC_TOKENS < n ? lo + SC_TOKENS : n;
+  const int hi = lo + span < n ? lo + span : n;
   const int back = taps - 1;
   const int pos0 = seq_pos0[b];
   float* st = state ? state + (size_t)seq_slot[b] * back * C + c : nullptr;
@@ -63,13 +63,22 @@ extern "C" int hb_short_conv(int out_dtype, const float* in, int ld_in, const fl
   HB_REQUIRE(taps >= 1 && taps - 1 <= SC_TOKENS, "short_conv: %d taps are outside the supported range 1..%d", taps, SC_TOKENS + 1);
   HB_REQUIRE(taps == 1 || state != nullptr, "short_conv: a convolution over more than one tap needs its state");
   HB_REQUIRE(n_seqs <= 65535 && ceil_div(max_q_len, SC_TOKENS) <= 65535, "short_conv: too many sequences or tokens per call");
-  dim3 grid(ceil_div(channels, SC_THREADS), ceil_div(max_q_len, SC_TOKENS), n_seqs);
+  // tokens per CTA: fewer while the grid would leave SMs without several CTAs (a CTA's tokens are a serial loop)
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int span = SC_TOKENS;
+  const int floor_span = taps - 1 > 8 ? taps - 1 : 8;
+  while (span / 2 >= floor_span &&
+         (long long)ceil_div(channels, SC_THREADS) * ceil_div(max_q_len, span) * n_seqs < 8LL * sms)
+    span /= 2;
+  dim3 grid(ceil_div(channels, SC_THREADS), ceil_div(max_q_len, span), n_seqs);
   if (out_dtype == HB_F32)
     hb_launch(short_conv_kernel<float>, grid, dim3(SC_THREADS), 0, (cudaStream_t)stream, in, ld_in, w, state, seq_slot, seq_start,
-              seq_pos0, (float*)out, ldo, channels, taps, add_input, act_silu);
+              seq_pos0, (float*)out, ldo, channels, taps, add_input, act_silu, span);
   else
     hb_launch(short_conv_kernel<bf16>, grid, dim3(SC_THREADS), 0, (cudaStream_t)stream, in, ld_in, w, state, seq_slot, seq_start,
-              seq_pos0, (bf16*)out, ldo, channels, taps, add_input, act_silu);
+              seq_pos0, (bf16*)out, ldo, channels, taps, add_input, act_silu, span);
   HB_CHECK_LAUNCH("short_conv");
   return 0;
 }

@@ -112,7 +112,7 @@ _SIGS = {
     "hb_delta_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p,
                          c_void_p, c_void_p, c_int, c_int, c_void_p],
     "hb_linear_scan": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_gated_rmsnorm": [c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                          c_int, c_void_p],
     "hb_qkv_rotary_cache": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_void_p, c_int, c_int, c_void_p,
@@ -598,7 +598,7 @@ def linear_scan(q, k, v, state, batch, out, heads, qk_heads, dk, dv, gates=None,
         raise BackendError("linear_scan: give the delta rule's gates or the constant decays")
     _run("hb_linear_scan", 1 if gates is not None else 0, q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(),
          v.stride(0), _ptr(gates), _ptr(decay), state.data_ptr(), batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(),
-         out.data_ptr(), out.stride(0), batch.n_seqs, int(heads), int(qk_heads), int(dk), int(dv), _stream())
+         out.data_ptr(), out.stride(0), batch.n_seqs, batch.max_q_len, int(heads), int(qk_heads), int(dk), int(dv), _stream())
 
 
 def gated_rmsnorm(o, w, eps, gate, out, units, n, sigmoid_gate=False) -> None:

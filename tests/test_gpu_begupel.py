@@ -235,6 +235,43 @@ def test_recurrences_in_steps_of_any_size(delta, H, G, dk, dv):
     assert float((state[1] - 7.0).abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("H,G,dk,dv", [(2, 1, 32, 16), (1, 1, 128, 128), (3, 3, 20, 9)])
+@pytest.mark.parametrize("lens", [[16], [32], [8], [15, 17], [47, 1, 9]])
+def test_delta_rule_over_many_tokens_with_gates_at_their_ends(lens, H, G, dk, dv):
+    """Steps long enough for the kernel that takes sixteen tokens at a time (whole groups, one token short, one over,
+    a single token beside long sequences), continued once from the state they left.  Some decays are exactly 0 (the
+    state is wiped there and nothing else is) or 1, some step sizes exactly 0 (the token writes nothing) or 1."""
+    g = torch.Generator().manual_seed(sum(lens) * dk + dv)
+    total = [2 * n for n in lens]
+    seqs = []
+    for n in total:
+        q, k, v = (torch.randn(n, G, dk, generator=g), torch.randn(n, G, dk, generator=g), torch.randn(n, H, dv, generator=g))
+        q, k = q / q.norm(dim=-1, keepdim=True), k / k.norm(dim=-1, keepdim=True)
+        gd, beta = torch.rand(n, H, generator=g) * 0.6 + 0.4, torch.rand(n, H, generator=g)
+        for t in range(n):
+            gd[t, t % H] = (0.0, 1.0, 1e-30)[t % 3] if t % 5 == 2 else gd[t, t % H]
+            beta[t, (t + 1) % H] = (0.0, 1.0)[t % 2] if t % 7 == 3 else beta[t, (t + 1) % H]
+        seqs.append((q, k, v, gd, beta))
+    state = torch.zeros(len(lens) + 1, H, dk, dv, device=DEV)
+    slots = list(range(len(lens), 0, -1))
+    got = [[] for _ in lens]
+    for r in range(2):
+        cat = lambda i: torch.cat([seqs[b][i][r * n:(r + 1) * n].reshape(n, -1) for b, n in enumerate(lens)]).to(DEV)   # noqa: E731
+        out = torch.zeros(sum(lens), H * dv, device=DEV)
+        ops.linear_scan(cat(0), cat(1), cat(2), state, step_of(lens, slots), out, H, G, dk, dv,
+                        gates=torch.cat([cat(3), cat(4)], dim=1).contiguous())
+        o = 0
+        for b, n in enumerate(lens):
+            got[b].append(out[o:o + n].cpu()); o += n
+    for b, n in enumerate(total):
+        q, k, v, gd, beta = (t.double() for t in seqs[b])
+        fin = []
+        ref = P.delta_recurrence(q, k, v, gd, beta, fin)
+        assert np.abs(torch.cat(got[b]).double().numpy() - ref.reshape(n, -1).numpy()).max() < 2e-5 * max(float(ref.abs().max()), 1.0), b
+        assert np.abs(to_np(state[slots[b]]) - torch.stack(fin).numpy()).max() < 2e-5 * max(float(torch.stack(fin).abs().max()), 1.0)
+    assert float(state[0].abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_unit_vectors_gates_output_norms_and_the_small_kernels(dtype):
     td = td_of(dtype)
