@@ -133,6 +133,10 @@ __global__ void __launch_bounds__(LS_THREADS) linear_scan_kernel(ScanArgs a) {
   __syncthreads();
   const bool wide = a.dk % 4 == 0 && a.ldq % 4 == 0 && a.ldk % 4 == 0 && (((uintptr_t)a.q | (uintptr_t)a.k) & 15) == 0;
   const float d = DELTA ? 0.0f : a.decay[h];
+  int st_lanes = 1;                                               // threads that copy one token's row of q and k
+  while (st_lanes < LS_THREADS && st_lanes * 4 < a.dk) st_lanes <<= 1;
+  const int st_row = tid / st_lanes, st_r = (tid % st_lanes) * 4;
+  const int cshift = 31 - __clz(cols);                            // cols is a power of two
 
   auto stage = [&](int buf, int c0) {
     float* qs = sh + buf * stage_floats;
@@ -140,13 +144,12 @@ __global__ void __launch_bounds__(LS_THREADS) linear_scan_kernel(ScanArgs a) {
     float* vs = ks + LS_CHUNK * DKP;
     float* gs = vs + LS_CHUNK * cols;
     const int n = t1 - c0 < LS_CHUNK ? t1 - c0 : LS_CHUNK;
-    if (wide) {
-      const int per = a.dk >> 2;
-      for (int i = tid; i < n * per; i += LS_THREADS) {
-        const int tt = i / per, r = (i - tt * per) * 4;
-        ls_copy16(qs + tt * DKP + r, a.q + (size_t)(c0 + tt) * a.ldq + qh * a.dk + r);
-        ls_copy16(ks + tt * DKP + r, a.k + (size_t)(c0 + tt) * a.ldk + qh * a.dk + r);
-      }
+    if (wide) {      // a power of two of threads per token's row, so no division stands in the loop
+      for (int tt = st_row; tt < n; tt += LS_THREADS / st_lanes)
+        for (int r = st_r; r < a.dk; r += st_lanes * 4) {
+          ls_copy16(qs + tt * DKP + r, a.q + (size_t)(c0 + tt) * a.ldq + qh * a.dk + r);
+          ls_copy16(ks + tt * DKP + r, a.k + (size_t)(c0 + tt) * a.ldk + qh * a.dk + r);
+        }
     } else {
       for (int i = tid; i < n * a.dk; i += LS_THREADS) {
         const int tt = i / a.dk, r = i - tt * a.dk;
@@ -155,7 +158,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_scan_kernel(ScanArgs a) {
       }
     }
     for (int i = tid; i < n * cols; i += LS_THREADS) {
-      const int tt = i / cols, c = blockIdx.z * cols + (i % cols);
+      const int tt = i >> cshift, c = blockIdx.z * cols + (i & (cols - 1));
       if (c < a.dv) ls_copy4(vs + i, a.v + (size_t)(c0 + tt) * a.ldv + h * a.dv + c);
     }
     if (DELTA)
@@ -234,7 +237,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_scan_kernel(ScanArgs a) {
       }
       __syncthreads();
       for (int i = tid; i < n * cols; i += LS_THREADS) {
-        const int tt = i / cols, c = i - tt * cols, cc = blockIdx.z * cols + c;
+        const int tt = i >> cshift, c = i & (cols - 1), cc = blockIdx.z * cols + c;
         if (cc < a.dv) {
           float o = red[tt * red_ld + c * R];
           for (int g = 1; g < R; ++g) o += red[tt * red_ld + c * R + g];
@@ -301,6 +304,10 @@ __global__ void __launch_bounds__(LS_THREADS) linear_scan_chunked_kernel(ScanArg
   __syncthreads();
   const bool wide = a.dk % 4 == 0 && a.ldq % 4 == 0 && a.ldk % 4 == 0 && (((uintptr_t)a.q | (uintptr_t)a.k) & 15) == 0;
   const float d = DELTA ? 0.0f : a.decay[h];
+  int st_lanes = 1;                                               // threads that copy one token's row of q and k
+  while (st_lanes < LS_THREADS && st_lanes * 4 < a.dk) st_lanes <<= 1;
+  const int st_row = tid / st_lanes, st_r = (tid % st_lanes) * 4;
+  const int cshift = 31 - __clz(cols);                            // cols is a power of two
 
   auto stage = [&](int buf, int c0) {
     float* qs = sh + buf * stage_floats;
@@ -308,13 +315,12 @@ __global__ void __launch_bounds__(LS_THREADS) linear_scan_chunked_kernel(ScanArg
     float* vs = ks + C * KS;
     float* gs = vs + C * cols;
     const int n = t1 - c0 < C ? t1 - c0 : C;
-    if (wide) {
-      const int per = a.dk >> 2;
-      for (int i = tid; i < n * per; i += LS_THREADS) {
-        const int tt = i / per, r = (i - tt * per) * 4;
-        ls_copy16(qs + tt * KS + r, a.q + (size_t)(c0 + tt) * a.ldq + qh * a.dk + r);
-        ls_copy16(ks + tt * KS + r, a.k + (size_t)(c0 + tt) * a.ldk + qh * a.dk + r);
-      }
+    if (wide) {      // a power of two of threads per token's row, so no division stands in the loop
+      for (int tt = st_row; tt < n; tt += LS_THREADS / st_lanes)
+        for (int r = st_r; r < a.dk; r += st_lanes * 4) {
+          ls_copy16(qs + tt * KS + r, a.q + (size_t)(c0 + tt) * a.ldq + qh * a.dk + r);
+          ls_copy16(ks + tt * KS + r, a.k + (size_t)(c0 + tt) * a.ldk + qh * a.dk + r);
+        }
     } else {
       for (int i = tid; i < n * a.dk; i += LS_THREADS) {
         const int tt = i / a.dk, r = i - tt * a.dk;
@@ -323,7 +329,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_scan_chunked_kernel(ScanArg
       }
     }
     for (int i = tid; i < n * cols; i += LS_THREADS) {
-      const int tt = i / cols, c = blockIdx.z * cols + (i % cols);
+      const int tt = i >> cshift, c = blockIdx.z * cols + (i & (cols - 1));
       if (c < a.dv) ls_copy4(vs + i, a.v + (size_t)(c0 + tt) * a.ldv + h * a.dv + c);
     }
     if (DELTA)
