@@ -536,6 +536,23 @@ OTHER = {
     "keys_wider_than_values": ([(U.parallel(heads=8, kv_heads=8, dim=128, vdim=32, window=32, rheads=2, rkv=2, rdim=128, rvdim=32), None),
                                 (U.lightning(heads=2, dim=128, vdim=32), U.dense(128))],
                                dict(vocab=200, width=128, groups=2, taps=4)),
+    # no layer keeps keys and values: the cache has states only
+    "recurrences_only": ([(U.lightning(heads=4, dim=32, vdim=64, decay=[0.0, 0.5, 0.99, 1.0]), U.dense(96)),
+                          (U.lightning(heads=2, dim=64, vdim=32), None),
+                          (U.lightning(heads=8, dim=16, vdim=16), U.dense(64))],
+                         dict(vocab=150, width=96, groups=3, taps=5, buckets=31, mul_prev=17, mul_cur=29)),
+    # every layer keeps keys and values, each with its own window, head count and head sizes; a window of one key
+    "attention_in_every_layer": ([(U.parallel(heads=4, kv_heads=1, dim=32, vdim=64, window=1, rot_dims=16, rheads=2, rkv=1, rdim=32, rvdim=64, conv=4), U.dense(80)),
+                                  (U.parallel(heads=2, kv_heads=2, dim=64, vdim=32, window=17, rot_dims=64, factor=None, rheads=4, rkv=4, rdim=16, rvdim=16, conv=2), None),
+                                  (U.parallel(heads=8, kv_heads=4, dim=16, vdim=16, window=None, rot_dims=0, rheads=8, rkv=2, rdim=64, rvdim=32, conv=5,
+                                              left_scale=-1.0, right_scale=0.25), U.dense(40))],
+                                 dict(vocab=90, width=80, groups=4, taps=3, buckets=7, mul_prev=-3, mul_cur=2)),
+    # nearer a real model's sizes: the tensor-core products and attention kernels, state matrices of 128 x 128
+    "larger": ([(U.lightning(heads=4, dim=128, vdim=128), U.dense(512)),
+                (U.parallel(heads=4, kv_heads=2, dim=128, vdim=128, window=100, rot_dims=64, rheads=4, rkv=2, rdim=128, rvdim=128), U.dense(512)),
+                (U.parallel(heads=8, kv_heads=8, dim=64, vdim=64, window=48, rheads=8, rkv=8, rdim=64, rvdim=64), None),
+                (U.lightning(heads=8, dim=64, vdim=32), None)],
+               dict(vocab=1000, width=512, groups=2, taps=4, buckets=4093, mul_prev=31, mul_cur=7, softcap=30.0)),
 }
 
 
