@@ -186,8 +186,8 @@ int hb_sample(const float* logits, int ld, int n_rows, int vocab, float temperat
 // group_norm.cu: RMS norm in groups (alone, or of a sublayer's result on its way into the stream), a gated activation with biases, a weighted sum of two arrays, a tanh cap
 int hb_group_rmsnorm(int dtype, const float* x, const float* w, void* out, const int* rows, int n_rows, int dim,
     int groups, float eps, void* stream);
-int hb_group_rmsnorm_residual(int dtype, const float* y, int ldy, const float* bias, const float* w, float* x,
-    void* h, int n_rows, int dim, int groups, float eps, void* stream);
+int hb_group_rmsnorm_residual(int dtype, const float* y, int ldy, const float* z, int ldz, float a, float b,
+    const float* bias, const float* w, float* x, void* h, int n_rows, int dim, int groups, float eps, void* stream);
 int hb_axpby(float* y, int ldy, float a, const float* z, int ldz, float b, int rows, int cols, void* stream);
 int hb_bias_glu(int dtype, const float* gu, int ld, const float* bias, void* out, int ldo, int n_tokens, int
     inter, int interleave, int act, void* stream);

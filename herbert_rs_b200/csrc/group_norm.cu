@@ -4,7 +4,8 @@
 //
 //   hb_group_rmsnorm           out[r] = GN(x[rows[r]] or x[r]) * w                (the norm before the head)
 //   hb_group_rmsnorm_residual  x += GN(y + bias) * w; h = x in the activation dtype   (a sublayer's result joins
-//                              the stream, and the next sublayer gets its input, in one pass)
+//                              the stream, and the next sublayer gets its input, in one pass); with a second array
+//                              z the normed vector is a * y + b * z (two mixers side by side, summed here)
 //   hb_axpby                   y = a * y + b * z                                  (two mixers side by side)
 //   hb_bias_glu                out = act(gate + b) * (up + b) from a product's float sums       (a gated feed-forward with biases)
 //   hb_tanh_cap                x = cap * tanh(x / cap)                            (a cap on the logits)
@@ -16,13 +17,16 @@
 #define GN_MAX_GROUPS 64
 template <typename T, bool RESIDUAL>
 __global__ void __launch_bounds__(256)
-group_rmsnorm_kernel(const float* __restrict__ y, int ldy, const float* __restrict__ bias, const float* __restrict__ w,
-                     float* __restrict__ x, T* __restrict__ out, const int* __restrict__ rows, int dim, int groups, float eps) {
+group_rmsnorm_kernel(const float* __restrict__ y, int ldy, const float* __restrict__ z, int ldz, float a, float b,
+                     const float* __restrict__ bias, const float* __restrict__ w, float* __restrict__ x, T* __restrict__ out,
+                     const int* __restrict__ rows, int dim, int groups, float eps) {
   __shared__ float sums[GN_MAX_GROUPS];
   pdl_wait();
   pdl_launch();
   const int r = blockIdx.x;
   const float* yr = y + (size_t)(rows ? rows[r] : r) * ldy;
+  const float* zr = z ? z + (size_t)r * ldz : nullptr;
+  auto value = [&](int i) { return (zr ? a * yr[i] + b * zr[i] : yr[i]) + (bias ? bias[i] : 0.0f); };
   const int n = dim / groups;
   for (int g = threadIdx.x; g < groups; g += blockDim.x) sums[g] = 0.0f;
   __syncthreads();
@@ -31,7 +35,7 @@ group_rmsnorm_kernel(const float* __restrict__ y, int ldy, const float* __restri
   for (int g = warp; g < groups; g += nwarp) {
     float s = 0.0f;
     for (int i = lane; i < n; i += 32) {
-      const float v = yr[g * n + i] + (bias ? bias[g * n + i] : 0.0f);
+      const float v = value(g * n + i);
       s = fmaf(v, v, s);
     }
     s = warp_sum(s);
@@ -40,7 +44,7 @@ group_rmsnorm_kernel(const float* __restrict__ y, int ldy, const float* __restri
   __syncthreads();
   for (int i = threadIdx.x; i < dim; i += blockDim.x) {
     const float inv = 1.0f / sqrtf(sums[i / n] / (float)n + eps);
-    const float v = ((yr[i] + (bias ? bias[i] : 0.0f)) * inv) * w[i];
+    const float v = (value(i) * inv) * w[i];
     if (RESIDUAL) {
       const float nx = x[(size_t)r * dim + i] + v;
       x[(size_t)r * dim + i] = nx;
@@ -60,25 +64,26 @@ extern "C" int hb_group_rmsnorm(int dtype, const float* x, const float* w, void*
              "group_rmsnorm: %d groups must divide the width %d and be at most %d", groups, dim, GN_MAX_GROUPS);
   if (dtype == HB_F32)
     hb_launch(group_rmsnorm_kernel<float, false>, dim3(n_rows), dim3(gn_threads(dim)), 0, (cudaStream_t)stream, x, dim,
-              (const float*)nullptr, w, (float*)nullptr, (float*)out, rows, dim, groups, eps);
+              (const float*)nullptr, 0, 1.0f, 0.0f, (const float*)nullptr, w, (float*)nullptr, (float*)out, rows, dim, groups, eps);
   else
     hb_launch(group_rmsnorm_kernel<bf16, false>, dim3(n_rows), dim3(gn_threads(dim)), 0, (cudaStream_t)stream, x, dim,
-              (const float*)nullptr, w, (float*)nullptr, (bf16*)out, rows, dim, groups, eps);
+              (const float*)nullptr, 0, 1.0f, 0.0f, (const float*)nullptr, w, (float*)nullptr, (bf16*)out, rows, dim, groups, eps);
   HB_CHECK_LAUNCH("group_rmsnorm");
   return 0;
 }
 
-extern "C" int hb_group_rmsnorm_residual(int dtype, const float* y, int ldy, const float* bias, const float* w, float* x,
-                                         void* h, int n_rows, int dim, int groups, float eps, void* stream) {
+extern "C" int hb_group_rmsnorm_residual(int dtype, const float* y, int ldy, const float* z, int ldz, float a, float b,
+                                         const float* bias, const float* w, float* x, void* h, int n_rows, int dim, int groups,
+                                         float eps, void* stream) {
   HB_REQUIRE(n_rows > 0 && dim > 0, "group_rmsnorm_residual: sizes must be positive");
   HB_REQUIRE(groups >= 1 && groups <= GN_MAX_GROUPS && dim % groups == 0,
              "group_rmsnorm_residual: %d groups must divide the width %d and be at most %d", groups, dim, GN_MAX_GROUPS);
   if (dtype == HB_F32)
-    hb_launch(group_rmsnorm_kernel<float, true>, dim3(n_rows), dim3(gn_threads(dim)), 0, (cudaStream_t)stream, y, ldy, bias, w,
-              x, (float*)h, (const int*)nullptr, dim, groups, eps);
+    hb_launch(group_rmsnorm_kernel<float, true>, dim3(n_rows), dim3(gn_threads(dim)), 0, (cudaStream_t)stream, y, ldy, z, ldz, a, b,
+              bias, w, x, (float*)h, (const int*)nullptr, dim, groups, eps);
   else
-    hb_launch(group_rmsnorm_kernel<bf16, true>, dim3(n_rows), dim3(gn_threads(dim)), 0, (cudaStream_t)stream, y, ldy, bias, w,
-              x, (bf16*)h, (const int*)nullptr, dim, groups, eps);
+    hb_launch(group_rmsnorm_kernel<bf16, true>, dim3(n_rows), dim3(gn_threads(dim)), 0, (cudaStream_t)stream, y, ldy, z, ldz, a, b,
+              bias, w, x, (bf16*)h, (const int*)nullptr, dim, groups, eps);
   HB_CHECK_LAUNCH("group_rmsnorm_residual");
   return 0;
 }

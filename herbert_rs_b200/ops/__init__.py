@@ -99,8 +99,8 @@ _SIGS = {
     "hb_moe_experts": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                        c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_group_rmsnorm": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
-    "hb_group_rmsnorm_residual": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
-                                  c_void_p],
+    "hb_group_rmsnorm_residual": [c_int, c_void_p, c_int, c_void_p, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_int, c_int, c_int, c_float, c_void_p],
     "hb_axpby": [c_void_p, c_int, c_float, c_void_p, c_int, c_float, c_int, c_int, c_void_p],
     "hb_bias_glu": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_tanh_cap": [c_void_p, c_int, c_float, c_int, c_int, c_void_p],
@@ -490,9 +490,10 @@ def group_rmsnorm(x, w, out, eps, groups=1, rows=None) -> None:
          x.shape[-1], int(groups), float(eps), _stream())
 
 
-def group_rmsnorm_residual(y, w, x, h, eps, groups, dtype, bias=None) -> None:
+def group_rmsnorm_residual(y, w, x, h, eps, groups, dtype, bias=None, second=None) -> None:
     """x += GN(y + bias) * w with GN the RMS norm in `groups` parts (bias [D] float or None); h, if given,
-    receives the updated x in the activation dtype `dtype`."""
+    receives the updated x in the activation dtype `dtype`.  With `second` = (z, a, b) the normed vector is
+    a * y + b * z + bias (z float, of y's shape)."""
     _check(y, torch.float32, "y"); _check(w, torch.float32, "w"); _check(x, torch.float32, "x")
     if h is not None:
         _check(h, dtype, "h")
@@ -500,8 +501,14 @@ def group_rmsnorm_residual(y, w, x, h, eps, groups, dtype, bias=None) -> None:
         _check(bias, torch.float32, "bias")
     if not x.is_contiguous() or (h is not None and not h.is_contiguous()):
         raise BackendError("group_rmsnorm_residual: x and h must be contiguous")
-    _run("hb_group_rmsnorm_residual", dtype_code(dtype), y.data_ptr(), y.stride(0), _ptr(bias), w.data_ptr(), x.data_ptr(),
-         _ptr(h), x.shape[0], x.shape[1], int(groups), float(eps), _stream())
+    z, a, b = second if second is not None else (None, 1.0, 0.0)
+    if z is not None:
+        _check(z, torch.float32, "z")
+        if z.shape != y.shape:
+            raise BackendError("group_rmsnorm_residual: the second array must have the first one's shape")
+    _run("hb_group_rmsnorm_residual", dtype_code(dtype), y.data_ptr(), y.stride(0), _ptr(z), z.stride(0) if z is not None else 0,
+         float(a), float(b), _ptr(bias), w.data_ptr(), x.data_ptr(), _ptr(h), x.shape[0], x.shape[1], int(groups), float(eps),
+         _stream())
 
 
 def axpby(y, a, z, b) -> None:

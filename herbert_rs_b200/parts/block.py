@@ -159,11 +159,14 @@ class SublayerNormBlock(Block):
             need = CacheNeed(need.kv, need.state, need.states + (("input_conv", conv),))
         return need
 
-    def _join(self, y, norm, scale, x, h, bias=None):
-        """x += norm(y + bias) (* scale); h, if given, receives the new x in the activation dtype."""
+    def _join(self, y, norm, scale, x, h, bias=None, second=None):
+        """x += norm(y + bias) (* scale); h, if given, receives the new x in the activation dtype.  `second` = (z, a, b):
+        the normed vector is a * y + b * z (an RMS norm takes the sum of two mixers side by side in the same pass)."""
         if norm.kind == "rmsnorm":
-            ops.group_rmsnorm_residual(y, norm.weight, x, h, norm.eps, norm.groups, self.rt.dtype, bias=bias)
+            ops.group_rmsnorm_residual(y, norm.weight, x, h, norm.eps, norm.groups, self.rt.dtype, bias=bias, second=second)
             return
+        if second is not None:
+            ops.axpby(y, second[1], second[0], second[2])
         if bias is not None:
             ops.add_row_bias(y, bias)
         ops.layernorm_residual(y, norm.weight, scale, x, h, norm.eps, self.rt.dtype)
@@ -180,9 +183,13 @@ class SublayerNormBlock(Block):
             h = ws.take(x.shape, dtype)
             ops.to_activation(x, h)
         y = ws.take(x.shape, torch.float32)
-        self.mixer.forward(h, y, batch, cache, accumulate=False)
+        second = None
+        if getattr(self.mixer, "forward_parts", None) is not None:
+            second = self.mixer.forward_parts(h, y, batch, cache)
+        else:
+            self.mixer.forward(h, y, batch, cache, accumulate=False)
         h2 = None if (wide or self.ffn is None) else ws.take(x.shape, dtype)
-        self._join(y, self.norm1, self.scale1, x, h2)
+        self._join(y, self.norm1, self.scale1, x, h2, second=second)
         if self.ffn is not None:
             bias = None
             if getattr(self.ffn, "take_output_bias", None) is not None and self.ffn.take_output_bias() is not None:

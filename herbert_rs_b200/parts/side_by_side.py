@@ -48,6 +48,14 @@ class SideBySideMixer(Mixer):
     def cache_need(self):
         return self.left.cache_need().merged(self.right.cache_need(), _RIGHT)
 
+    def forward_parts(self, h, y, batch, cache):
+        """Both results apart: the left one into y, the right one into a float array z that is returned with the two
+        constants, for a caller whose next kernel can take a * y + b * z as its input (a block that norms the sum)."""
+        self.left.forward(h, y, batch, cache, accumulate=False)
+        z = self.rt.workspace.take(y.shape, torch.float32)
+        self.right.forward(h, z, batch, cache.sub(_RIGHT), accumulate=False)
+        return z, self.a, self.b
+
     def forward(self, h, residual, batch, cache, accumulate=True):
         ws = self.rt.workspace
         y = residual if not accumulate else ws.take(residual.shape, torch.float32)

@@ -73,6 +73,14 @@ def test_rms_norm_in_groups_alone_and_on_the_way_into_the_stream(dtype, dim, gro
         ref = x.double() + P.group_norm(yy, w.double(), groups, 1e-5)
         assert_close(to_np(x1), ref.numpy(), "float32", "stream")
         assert_close(to_np(h), ref.numpy(), dtype, "next input")
+    # the sum of two arrays with two constants, normed in the same pass
+    z = torch.randn(7, dim + 3, generator=g) * 2.0
+    x1, h = x.clone().to(DEV), torch.empty(7, dim, dtype=td_of(dtype), device=DEV)
+    ops.group_rmsnorm_residual(y.to(DEV)[:, :dim], w.to(DEV), x1, h, 1e-5, groups, td_of(dtype), bias=bias.to(DEV),
+                               second=(z.to(DEV)[:, :dim], 1.25, -0.6))
+    ref = x.double() + P.group_norm(1.25 * y.double()[:, :dim] - 0.6 * z.double()[:, :dim] + bias.double(), w.double(), groups, 1e-5)
+    assert_close(to_np(x1), ref.numpy(), "float32", "stream, two arrays")
+    assert_close(to_np(h), ref.numpy(), dtype, "next input, two arrays")
     if groups > 1:       # one norm over the whole row is something else
         assert (P.group_norm(x.double(), w.double(), groups, 1e-5) - P.group_norm(x.double(), w.double(), 1, 1e-5)).abs().max() > 1e-2
 
