@@ -6,13 +6,16 @@
 //
 // The state of a sequence lives in its slot of the cache's state region ([slots][heads][dk][dv] floats, zero when
 // the slot is handed out): a step reads it, runs its tokens in order and writes it back, so a prompt in one step,
-// in pieces or token by token performs the same float operations in the same order.  Query/key head of value head
-// h: h / (heads / qk_heads).  Everything here is float on both paths.
+// in pieces or token by token computes the same recurrence; the order in which a sum over the key channels is
+// taken follows the launch (lanes per column, tokens one by one or sixteen at a time), so two cuttings agree to
+// float rounding, not to the bit.  Query/key head of value head h: h / (heads / qk_heads).  Everything here is
+// float on both paths.
 //
 //   hb_silu_columns     in place: x <- silu(x) on a range of columns of float rows
 //   hb_delta_prepare    q, k -> unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q also times qscale;
 //                       beta = sigmoid(b);  g = exp(-exp(A_log) * softplus(a + dt_bias))
-//   hb_linear_scan      the recurrence
+//   hb_linear_scan      the recurrence: token by token (decode, short steps, several sequences), or for one long
+//                       prompt alone the delta rule sixteen tokens at a time
 //   hb_gated_rmsnorm    y = o / rms(o) * w * gate-activation(g), the norm per head (w [dv]) or over all heads (w [H dv])
 #include "api.h"
 #include "common.cuh"
