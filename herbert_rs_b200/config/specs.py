@@ -66,13 +66,17 @@ class ScaledRotarySpec:
 class RotaryPairsSpec:
     """Rotary pairs whose angles are computed from the position (no table): pair m of `rotary_dim`
     channels turns by p * theta^(-2m/rotary_dim) / linear_factor.  layout "interleaved": pair m is
-    channels (2m, 2m + 1); "halves": (m, m + rotary_dim/2).  Channels beyond rotary_dim pass unchanged."""
+    channels (2m, 2m + 1); "halves": (m, m + rotary_dim/2).  Channels beyond rotary_dim pass unchanged.
+    `band_scaling` (factor, low, high, original) changes the frequencies band by band: with the wavelength
+    l = 2 pi / f, f stays where l < original / high, becomes f / factor where l > original / low, and in between
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
 
     rotary_dim: int
     theta: float
     linear_factor: float = 1.0
     layout: str = "interleaved"
     kind: str = "rope_pairs"
+    band_scaling: Optional[tuple] = None
 
 
 @dataclass(frozen=True)
@@ -156,6 +160,24 @@ class AttentionSpec:
     whole_qk_norm: bool = False
     value_rotation: Optional[RotaryPairsSpec] = None
     norm_names: tuple = ("q_norm.weight", "k_norm.weight")
+    # Further options of that form (each takes it):
+    # `key_weights` "sigmoid": no softmax; a visible key weighs sigmoid(score + b) with a learned b per query head
+    #     (tensor `key_bias_name`), and the weights are not normalised over the keys;
+    # `conv_taps`: q, k and v each pass a short causal convolution over time, channel by channel, right after the
+    #     projection (tensors named as the matrices with `conv_suffix`, [channels, taps], the last column weighs the
+    #     token itself); a sequence's last taps - 1 projected rows are state;
+    # `head_gate`: a head's result is multiplied by sigmoid(G h), one number per token and head (tensor `head_gate_name`);
+    # `reads_kv`: the mixer has no key and value tensors: its schedule step reads what another step stored;
+    # `cache_window`: how many of the last keys the cache must keep, where that differs from the mixer's own window
+    #     (another step with a longer window reads this one's keys); -1: the mixer's window, None: every key.
+    key_weights: str = "softmax"
+    key_bias_name: str = "pb"
+    conv_taps: Optional[int] = None
+    conv_suffix: str = ".conv"
+    head_gate: bool = False
+    head_gate_name: str = "g"
+    reads_kv: bool = False
+    cache_window: Optional[int] = -1
 
 
 @dataclass(frozen=True)
@@ -192,6 +214,38 @@ class GatedDeltaSpec:
     norm_eps: float
     kind: str = "gated_delta"
     unit_eps: float = 1e-6      # inside the root of the unit vectors' length
+
+
+@dataclass(frozen=True)
+class GeneralDeltaSpec:
+    """The generalised delta rule: per head S <- diag(w) S - (a * u) (u^T S) + k v^T (both terms read the old S),
+    o = S^T r, with u = k / sqrt(sum k^2 + unit_eps) per head, a decay per head and key channel
+    w = exp(-decay_constant * sigmoid(W2 tanh(W1 h) + w0)) and a removal rate a = sigmoid(A h + a0) likewise;
+    r, k, v = R h, K h, V h.  Each head's o is divided by its root mean square, the heads side by side are
+    multiplied by a weight (one number per head and channel) and by sigmoid(G h), then projected.  The decay's
+    inner width is the stored tensor's."""
+
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    norm_eps: float
+    decay_constant: float
+    unit_eps: float = 1e-6
+    kind: str = "general_delta"
+    names: tuple = ()          # pairs (role, tensor name) that replace the mixer's defaults
+
+
+@dataclass(frozen=True)
+class TokenSideSpec:
+    """A second input chosen by the token, added at the end of a layer: e = table[token][column0 : column0 + dim];
+    y = P (gelu_tanh(G x) * e); x <- x + y / sqrt(mean(y^2) + eps) * w.  `names`: G, P and w under the block's prefix.
+    The table belongs to the model (`ModelSpec.token_side_table`); a layer reads its own columns of it."""
+
+    dim: int
+    column0: int
+    eps: float
+    names: tuple = ("side.gate", "side.proj", "side.norm")
 
 
 @dataclass(frozen=True)
@@ -246,7 +300,8 @@ class RoutedFFSpec:
     `group_top`: the experts form `groups` equal groups of neighbours, a group's score is the sum of its
     `group_top` largest scores, and only experts of the `keep_groups` best groups can be chosen;
     `weight_scale`: a factor on every chosen weight; `shared`: a dense gated feed-forward (its own
-    spec, which also names its tensors) that runs for every token and is added."""
+    spec, which also names its tensors) that runs for every token and is added.  activation "swish_clamp" (gated
+    experts only) takes `act_limit` L: g = min(gate, L), u = clamp(up, -L, L), hidden = g sigmoid(1.702 g) (u + 1)."""
 
     hidden_size: int
     num_experts: int
@@ -264,6 +319,7 @@ class RoutedFFSpec:
     group_top: int = 2
     weight_scale: float = 1.0
     shared: Optional[SwiGLUSpec] = None
+    act_limit: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -278,6 +334,11 @@ class BlockSpec:
     channel (tensor `input_conv_name`, [width, taps], the last column weighs the token itself).
     kind "parallel": h = norm1(x); out = x + residual_mult * (mixer(h) + ffn(h)): one norm, both
     sublayers read its result; `ffn` may be None; norm2 is unused (None).
+    kind "sandwich": a norm before and after each sublayer, h = norm1(x); x <- x + post1(mixer(h) * gate1);
+    h = norm2(x); x <- x + post2(ffn(h) * gate2): `post_norms` are the two norms of the results, `residual_gates`
+    (None: no gates) names two matrices R with biases (R's name + `residual_gate_bias`): gate = sigmoid(R h + b), a
+    number per channel, from the same h the sublayer reads; `ffn` may be None; `token_side` adds a token's own second
+    input at the layer's end.
     `names` maps the block's local part names to the sub-prefixes used in tensor names.
     """
 
@@ -290,6 +351,10 @@ class BlockSpec:
     residual_mult: float = 1.0
     input_conv_taps: Optional[int] = None
     input_conv_name: str = "canon1"
+    post_norms: Optional[tuple] = None
+    residual_gates: Optional[tuple] = None
+    residual_gate_bias: str = ".b"
+    token_side: Optional[TokenSideSpec] = None
     names: tuple = (
         ("norm1", "input_layernorm"),
         ("mixer", "self_attn"),
@@ -341,6 +406,8 @@ class ModelSpec:
     pair_embedding: Optional[PairEmbeddingSpec] = None
     # c: logits <- c * tanh(logits / c)
     logit_softcap: Optional[float] = None
+    # (tensor name, columns): a second table [vocab, columns] of which blocks with a `token_side` read their columns
+    token_side_table: Optional[tuple] = None
     extra: dict = field(default_factory=dict)     # free for an architecture's own model class
 
 

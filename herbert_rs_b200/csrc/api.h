@@ -23,13 +23,17 @@ extern "C" {
 #define HB_ACT_GELU_TANH 1  // 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
 #define HB_ACT_GELU 2       // 0.5 z (1 + erf(z / sqrt(2)))
 #define HB_ACT_RELU 3       // max(z, 0)
+// gated experts only, with a limit L: g' = min(gate, L), u' = clamp(up, -L, L); g' sigmoid(1.702 g') (u' + 1)
+#define HB_ACT_SWISH_CLAMP 4
+#define HB_SWISH_CLAMP_SLOPE 1.702f
 
 
 // attention_decode.cu: decode attention over the paged cache (one query per sequence, keys cut into splits)
 long long hb_attention_decode_scratch_floats(int n_seqs, int nh, int hd, int nsplit);
 int hb_attention_decode_bf16(const void* q, int ldq, void* out, int ldo, const void* kcache, const void* vcache,
     const int* seq_len, const int* seq_pages, int pages_stride, float* scratch, int n_seqs, int nh, int nkv, int hd,
-    int page_size, int nsplit, float scale, int window, float softcap, const float* sink, void* stream);
+    int page_size, int nsplit, float scale, int window, float softcap, const float* sink, const float* gate_bias, void*
+    stream);
 int hb_attention_decode_fused_bf16(const void* qkv, int ld, void* out, int ldo, void* kcache, void* vcache,
     const float* qw, const float* kw, float eps, const float* cos_tab, const float* sin_tab, int table_rows,
     int write_cache, const int* seq_len, const int* seq_pages, int pages_stride, float* scratch, int*
@@ -38,7 +42,8 @@ int hb_attention_decode_fused_bf16(const void* qkv, int ld, void* out, int ldo, 
 // attention_prefill.cu: prefill attention, mma.sync flash form, head sizes in steps of 16 up to 256
 int hb_attention_prefill_bf16(const void* q, int ldq, void* out, int ldo, const void* kcache, const void* vcache,
     const int* seq_start, const int* seq_pos0, const int* seq_pages, int pages_stride, int n_seqs, int max_q_len, int
-    nh, int nkv, int hd, int page_size, float scale, int window, float softcap, const float* sink, void* stream);
+    nh, int nkv, int hd, int page_size, float scale, int window, float softcap, const float* sink, const float*
+    gate_bias, void* stream);
 
 // attention_prefill_tc.cu: prefill attention on tcgen05 tensor cores, head sizes 64 and 128
 int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens, void* out, int ldo, const void* kcache,
@@ -49,7 +54,8 @@ int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens, void* out
 // attention_simt.cu: attention of any shape on the CUDA cores (the 32-bit path)
 int hb_attention_simt(int dtype, const void* q, int ldq, void* out, int ldo, const void* kcache, const void*
     vcache, const int* tok_seq, const int* tok_pos, const int* seq_pages, int pages_stride, int n_tokens, int nh, int
-    nkv, int hd, int page_size, float scale, int window, float softcap, const float* sink, void* stream);
+    nkv, int hd, int page_size, float scale, int window, float softcap, const float* sink, const float* gate_bias,
+    void* stream);
 
 // elementwise.cu: embedding, RMSNorm, SwiGLU, head norm + rotation + cache write, residual sum, shared-norm finish
 int hb_embed(int dtype, const void* table, const int* ids, float* out, int n_tokens, int hidden, int vocab, float
@@ -156,8 +162,8 @@ int hb_layernorm_residual(int dtype, const float* y, int ldy, const float* w, co
 int hb_moe_route(int dtype, const void* h, int ld, const void* w_router, int* ids, float* weights, int n_tokens,
     int D, int E, int top, int renorm, int sigmoid, int groups, int keep, int group_top, float wscale, void* stream);
 int hb_moe_experts(int dtype, const void* h, int ld, const void* up, const void* down, const int* ids, const
-    float* weights, void* mid, float* y, int ldy, int n_tokens, int D, int F, int top, int act, int gated, int
-    accumulate, void* stream);
+    float* weights, void* mid, float* y, int ldy, int n_tokens, int D, int F, int top, int act, int gated, float
+    act_limit, int accumulate, void* stream);
 long long hb_moe_grouped_scratch_ints(int n_tokens, int E, int top);
 int hb_moe_experts_tc_rows(int n_tokens, int E, int top);
 int hb_moe_experts_tc_bf16(const void* h, int ld, const void* up, const void* down, const int* ids, const float*
@@ -165,7 +171,7 @@ int hb_moe_experts_tc_bf16(const void* h, int ld, const void* up, const void* do
     int top, int accumulate, int* error_flag, void* stream);
 int hb_moe_experts_grouped_bf16(const void* h, int ld, const void* up, const void* down, const int* ids, const
     float* weights, int* scratch, void* mid, float* part, float* y, int ldy, int n_tokens, int D, int E, int F, int
-    top, int act, int gated, int accumulate, void* stream);
+    top, int act, int gated, float act_limit, int accumulate, void* stream);
 
 // qk_prepare.cu: biases, query temperature and cache write for a mixer that neither norms nor rotates its heads
 int hb_qk_prepare_cache(int dtype, const float* qkv, int ld, const float* bias, void* q_out, int ldq, float
@@ -210,7 +216,7 @@ int hb_linear_scan(int delta, const float* q, int ldq, const float* k, int ldk, 
     float* gates, const float* decay, float* state, const int* seq_slot, const int* seq_start, float* out, int ldo,
     int n_seqs, int max_q_len, int heads, int qk_heads, int dk, int dv, void* stream);
 int hb_gated_rmsnorm(int dtype, const float* o, int ldo, const float* w, float eps, const float* gate, int ldg,
-    void* y, int ldy, int n_tokens, int units, int n, int act, void* stream);
+    void* y, int ldy, int n_tokens, int units, int n, int act, int w_stride, void* stream);
 
 // rotary_pairs.cu: whole-projection q/k norm, rotation of pairs by position (q, k and v), cache write; the turn back of the results
 int hb_qkv_rotary_cache(int dtype, const float* rows, int ld, const float* wq, const float* wk, float eps, int
@@ -219,6 +225,21 @@ int hb_qkv_rotary_cache(int dtype, const float* rows, int ld, const float* wq, c
     int nkv, int dk, int dv, int hd, int page_size, int write_cache, void* stream);
 int hb_rotate_heads_back(int dtype, const void* att, int ld, int hd, const float* fv, int halves, const int*
     tok_pos, void* y, int ldy, int n_tokens, int nh, int dv, void* stream);
+int hb_head_gate(int dtype, const void* att, int ld, int hd, const float* gate, int ldg, void* y, int ldy, int
+    n_tokens, int nh, int dv, void* stream);
+
+// general_delta.cu: the generalised delta rule (decay per key channel, removal along the unit key): its vectors, its recurrence
+int hb_general_delta_prepare(int dtype, const float* rows, int ld, int r_off, int k_off, int a_off, int low_off,
+    const void* w2, const float* w0, const float* a0, float decay_c, float unit_eps, float* prep, int n_tokens, int
+    heads, int dk, int rank, void* stream);
+int hb_general_delta_scan(const float* prep, const float* v, int ldv, float* state, const int* seq_slot, const int*
+    seq_start, float* out, int ldo, int n_seqs, int heads, int dk, int dv, void* stream);
+
+// gated_residual.cu: a sublayer's result through a sigmoid gate and an RMS norm into the stream (+ the next norm); a gate chosen by the token's id
+int hb_gated_norm_residual(int dtype, const float* y, int ldy, const float* z, int ldz, const float* zb, const float*
+    w, float eps, float* x, const float* w2, float eps2, void* h, int n_rows, int D, void* stream);
+int hb_token_gate(int dtype, const float* s, int lds, const void* table, int ldt, int col0, const int* ids, void*
+    out, int ldo, int n_tokens, int m, int vocab, void* stream);
 
 #ifdef __cplusplus
 }

@@ -44,6 +44,8 @@ struct DecodeArgs {
   int window;
   int stages;
   float softcap;       // > 0: score <- softcap * tanh(score / softcap) after the scale
+  const float* gate_bias;  // [nh] or null.  Not null: no softmax; a visible key weighs sigmoid(score + gate_bias[h]) as it
+                           // is.  Every running maximum then stays 0, so splits and warps simply add up (general kernel only)
 };
 
 // What the fused variant of the keys-as-M kernel needs besides: it takes the raw q/k/v row of each
@@ -163,6 +165,13 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
   }
 
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};   // heads g and g + 8
+  const bool gated = a.gate_bias != nullptr;
+  float gb[2] = {0.0f, 0.0f};
+  if (gated) {
+    m[0] = m[1] = 0.0f;
+    if (g < G) gb[0] = a.gate_bias[kvh * G + g];
+    if (g + 8 < G) gb[1] = a.gate_bias[kvh * G + g + 8];
+  }
   float o[HDM / 8][4];
 #pragma unroll
   for (int i = 0; i < HDM / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
@@ -210,29 +219,37 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
           s[nt][j] = v;
           mx[j >> 1] = fmaxf(mx[j >> 1], v);
         }
-      float corr[2];
+      float corr[2] = {1.0f, 1.0f};
+      if (gated) {
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-        const float m_new = fmaxf(m[r], mx[r]);
-        corr[r] = (m_new == -INFINITY) ? 1.0f : __expf(m[r] - m_new);
-        m[r] = m_new;
-      }
-      float ps[2] = {0.0f, 0.0f};
+        for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float pv = (s[nt][j] == -INFINITY) ? 0.0f : __expf(s[nt][j] - m[j >> 1]);
-          s[nt][j] = pv;
-          ps[j >> 1] += pv;
+          for (int j = 0; j < 4; ++j)
+            s[nt][j] = (s[nt][j] == -INFINITY) ? 0.0f : __fdividef(1.0f, 1.0f + __expf(-(s[nt][j] + gb[j >> 1])));
+      } else {
+  #pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+          mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+          const float m_new = fmaxf(m[r], mx[r]);
+          corr[r] = (m_new == -INFINITY) ? 1.0f : __expf(m[r] - m_new);
+          m[r] = m_new;
         }
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        ps[r] += __shfl_xor_sync(0xffffffffu, ps[r], 1);
-        ps[r] += __shfl_xor_sync(0xffffffffu, ps[r], 2);
-        l[r] = l[r] * corr[r] + ps[r];
+        float ps[2] = {0.0f, 0.0f};
+  #pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+  #pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float pv = (s[nt][j] == -INFINITY) ? 0.0f : __expf(s[nt][j] - m[j >> 1]);
+            s[nt][j] = pv;
+            ps[j >> 1] += pv;
+          }
+  #pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          ps[r] += __shfl_xor_sync(0xffffffffu, ps[r], 1);
+          ps[r] += __shfl_xor_sync(0xffffffffu, ps[r], 2);
+          l[r] = l[r] * corr[r] + ps[r];
+        }
       }
       const unsigned pa0 = pack_bf16(s[0][0], s[0][1]), pa1 = pack_bf16(s[0][2], s[0][3]);
       const unsigned pa2 = pack_bf16(s[1][0], s[1][1]), pa3 = pack_bf16(s[1][2], s[1][3]);
@@ -647,7 +664,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
 // denominator here, once, whatever the number of splits: m covers it and e^{sink - m} is added.
 __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                 bf16* __restrict__ out, int ldo, int nh, int hd, int nsplit,
-                                                const float* __restrict__ sink) {
+                                                const float* __restrict__ sink, int gated) {
   pdl_wait();
   pdl_launch();
   const int h = blockIdx.x, b = blockIdx.y;
@@ -659,7 +676,7 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o
     const float ms = part_ml[(base + s) * 2];
     if (ms != -INFINITY) ll += __expf(ms - mm) * part_ml[(base + s) * 2 + 1];
   }
-  const float inv = ll > 0.0f ? 1.0f / ll : 0.0f;
+  const float inv = gated ? 1.0f : (ll > 0.0f ? 1.0f / ll : 0.0f);    // sigmoid weights: every m is 0, the partial sums add up
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float acc = 0.0f;
     for (int s = 0; s < nsplit; ++s) {
@@ -688,9 +705,10 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
                                         const void* vcache, const int* seq_len, const int* seq_pages,
                                         int pages_stride, float* scratch, int n_seqs, int nh, int nkv, int hd,
                                         int page_size, int nsplit, float scale, int window, float softcap,
-                                        const float* sink, void* stream) {
+                                        const float* sink, const float* gate_bias, void* stream) {
   HB_REQUIRE(n_seqs > 0 && nh > 0 && nkv > 0 && hd > 0, "attention_decode: sizes must be positive");
   HB_REQUIRE(softcap >= 0.0f, "attention_decode: the cap on the scores must be >= 0 (0: none)");
+  HB_REQUIRE(gate_bias == nullptr || sink == nullptr, "attention_decode: sigmoid weights have no sink");
   HB_REQUIRE(nh % nkv == 0, "attention_decode: %d query heads are not a multiple of %d key/value heads", nh, nkv);
   HB_REQUIRE(nh / nkv <= 16, "attention_decode: at most 16 query heads per key/value head, got %d", nh / nkv);
   HB_REQUIRE(hd % 16 == 0 && hd <= 256, "attention_decode: head size %d must be a multiple of 16, at most 256", hd);
@@ -707,14 +725,14 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
   float* part_o = scratch;
   float* part_ml = scratch + (size_t)n_seqs * nh * nsplit * hd;
   DecodeArgs a{(const bf16*)q, ldq, (const bf16*)kcache, (const bf16*)vcache, seq_len, seq_pages, pages_stride,
-               part_o, part_ml, nh, nkv, hd, page_size, nsplit, scale, window, stages, softcap};
+               part_o, part_ml, nh, nkv, hd, page_size, nsplit, scale, window, stages, softcap, gate_bias};
   dim3 grid(nsplit, nkv, n_seqs);
   cudaError_t e;
   if (hd <= 64) {
     e = cudaFuncSetAttribute(attention_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     hb_launch(attention_decode_kernel<64>, dim3(grid), dim3(AD_THREADS), smem, s, a);
-  } else if (hd == 128) {
+  } else if (hd == 128 && gate_bias == nullptr) {
     if (nh / nkv <= 8) {
       e = cudaFuncSetAttribute(attention_decode_km_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
@@ -724,7 +742,7 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
       if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
       hb_launch(attention_decode_km_kernel<2, false>, dim3(grid), dim3(AD_THREADS), smem, s, a, DecodeFuse{});
     }
-  } else if (hd < 128) {
+  } else if (hd <= 128) {
     e = cudaFuncSetAttribute(attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     hb_launch(attention_decode_kernel<128>, dim3(grid), dim3(AD_THREADS), smem, s, a);
@@ -735,7 +753,7 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
   }
   HB_CHECK_LAUNCH("attention_decode");
   dim3 cgrid(nh, n_seqs);
-  hb_launch(attention_decode_combine_kernel, dim3(cgrid), dim3(hd >= 128 ? 128 : 64), 0, s, part_o, part_ml, (bf16*)out, ldo, nh, hd, nsplit, sink);
+  hb_launch(attention_decode_combine_kernel, dim3(cgrid), dim3(hd >= 128 ? 128 : 64), 0, s, part_o, part_ml, (bf16*)out, ldo, nh, hd, nsplit, sink, gate_bias != nullptr ? 1 : 0);
   HB_CHECK_LAUNCH("attention_decode_combine");
   return 0;
 }

@@ -42,6 +42,7 @@ struct PrefillArgs {
   int stages;
   float softcap;       // > 0: score <- softcap * tanh(score / softcap) after the scale
   const float* sink;   // [nh] or null: e^{sink} joins the row's sum (m starts at the sink, l at 1)
+  const float* gate_bias;  // [nh] or null.  Not null: no softmax; a visible key weighs sigmoid(score + gate_bias[h]) as it is
 };
 
 template <int HDM>
@@ -138,6 +139,8 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(PrefillAr
     m[0] = m[1] = a.sink[h];
     l[0] = l[1] = 1.0f;
   }
+  const bool gated = a.gate_bias != nullptr;
+  const float gb = gated ? a.gate_bias[h] : 0.0f;
   float o[HDM / 8][4];
 #pragma unroll
   for (int i = 0; i < HDM / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
@@ -192,33 +195,42 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(PrefillAr
           s[nt][j] = v;
           mx[j >> 1] = fmaxf(mx[j >> 1], v);
         }
-      float corr[2];
+      if (gated) {
+        // sigmoid weights: nothing is normalised, so there is no running maximum, no running sum and no rescaling
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-        const float m_new = fmaxf(m[r], mx[r]);
-        corr[r] = (m_new == -INFINITY) ? 1.0f : __expf(m[r] - m_new);
-        m[r] = m_new;
-      }
-      float ps[2] = {0.0f, 0.0f};
+        for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float pv = (s[nt][j] == -INFINITY) ? 0.0f : __expf(s[nt][j] - m[j >> 1]);
-          s[nt][j] = pv;
-          ps[j >> 1] += pv;
+          for (int j = 0; j < 4; ++j)
+            s[nt][j] = (s[nt][j] == -INFINITY) ? 0.0f : __fdividef(1.0f, 1.0f + __expf(-(s[nt][j] + gb)));
+      } else {
+        float corr[2];
+  #pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+          mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+          const float m_new = fmaxf(m[r], mx[r]);
+          corr[r] = (m_new == -INFINITY) ? 1.0f : __expf(m[r] - m_new);
+          m[r] = m_new;
         }
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        ps[r] += __shfl_xor_sync(0xffffffffu, ps[r], 1);
-        ps[r] += __shfl_xor_sync(0xffffffffu, ps[r], 2);
-        l[r] = l[r] * corr[r] + ps[r];
-      }
-#pragma unroll
-      for (int nd = 0; nd < HDM / 8; ++nd) {
-        o[nd][0] *= corr[0]; o[nd][1] *= corr[0]; o[nd][2] *= corr[1]; o[nd][3] *= corr[1];
+        float ps[2] = {0.0f, 0.0f};
+  #pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+  #pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float pv = (s[nt][j] == -INFINITY) ? 0.0f : __expf(s[nt][j] - m[j >> 1]);
+            s[nt][j] = pv;
+            ps[j >> 1] += pv;
+          }
+  #pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          ps[r] += __shfl_xor_sync(0xffffffffu, ps[r], 1);
+          ps[r] += __shfl_xor_sync(0xffffffffu, ps[r], 2);
+          l[r] = l[r] * corr[r] + ps[r];
+        }
+  #pragma unroll
+        for (int nd = 0; nd < HDM / 8; ++nd) {
+          o[nd][0] *= corr[0]; o[nd][1] *= corr[0]; o[nd][2] *= corr[1]; o[nd][3] *= corr[1];
+        }
       }
       // ---- O += P V : four 16-key slices -----------------------------------------------------------------
 #pragma unroll
@@ -242,7 +254,7 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(PrefillAr
   }
   cp_async_wait<0>();
 
-  const float inv0 = l[0] > 0.0f ? 1.0f / l[0] : 0.0f, inv1 = l[1] > 0.0f ? 1.0f / l[1] : 0.0f;
+  const float inv0 = gated ? 1.0f : (l[0] > 0.0f ? 1.0f / l[0] : 0.0f), inv1 = gated ? 1.0f : (l[1] > 0.0f ? 1.0f / l[1] : 0.0f);
   bf16* o0 = a.out + (size_t)(row0 + qi0) * a.ldo + (size_t)h * hd;
   bf16* o1 = a.out + (size_t)(row0 + qi1) * a.ldo + (size_t)h * hd;
 #pragma unroll
@@ -259,7 +271,7 @@ extern "C" int hb_attention_prefill_bf16(const void* q, int ldq, void* out, int 
                                          const void* vcache, const int* seq_start, const int* seq_pos0,
                                          const int* seq_pages, int pages_stride, int n_seqs, int max_q_len,
                                          int nh, int nkv, int hd, int page_size, float scale, int window, float softcap,
-                                         const float* sink, void* stream) {
+                                         const float* sink, const float* gate_bias, void* stream) {
   HB_REQUIRE(n_seqs > 0 && max_q_len > 0 && nh > 0 && nkv > 0 && hd > 0, "attention_prefill: sizes must be positive");
   HB_REQUIRE(nh % nkv == 0, "attention_prefill: %d query heads are not a multiple of %d key/value heads", nh, nkv);
   HB_REQUIRE(hd % 16 == 0 && hd <= 256, "attention_prefill: head size %d must be a multiple of 16, at most 256", hd);
@@ -270,6 +282,7 @@ extern "C" int hb_attention_prefill_bf16(const void* q, int ldq, void* out, int 
   HB_REQUIRE(nh <= 65535 && n_seqs <= 65535, "attention_prefill: grid too large");
   HB_REQUIRE(softcap >= 0.0f, "attention_prefill: the cap on the scores must be >= 0 (0: none)");
   HB_REQUIRE(window >= 0, "attention_prefill: window must be >= 0");
+  HB_REQUIRE(gate_bias == nullptr || sink == nullptr, "attention_prefill: sigmoid weights have no sink");
   HB_REQUIRE((long long)pages_stride * (page_size / AP_TILE) <= AP_PAGE_IDS, "attention_prefill: sequences of more than %d keys are not supported", AP_PAGE_IDS * AP_TILE);
   int stages = 3;
   int smem = stages * 2 * AP_TILE * (hd * 2 + 16);
@@ -278,7 +291,7 @@ extern "C" int hb_attention_prefill_bf16(const void* q, int ldq, void* out, int 
     smem = stages * 2 * AP_TILE * (hd * 2 + 16);
   }
   PrefillArgs a{(const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)kcache, (const bf16*)vcache, seq_start, seq_pos0,
-                seq_pages, pages_stride, nh, nkv, hd, page_size, scale, window, stages, softcap, sink};
+                seq_pages, pages_stride, nh, nkv, hd, page_size, scale, window, stages, softcap, sink, gate_bias};
   dim3 grid(ceil_div(max_q_len, AP_QTILE), nh, n_seqs);
   cudaStream_t s = (cudaStream_t)stream;
   cudaError_t e;

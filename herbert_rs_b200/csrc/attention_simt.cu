@@ -13,6 +13,8 @@
 // (softcap > 0), and a sink, a learned number per query head whose exponential joins the softmax's
 // denominator and nothing else: the running maximum starts at the sink and the running sum at 1,
 // as if it were a first key without a value.  The value plane may be the key plane itself.
+// A third option replaces the softmax: with `gate_bias` (a number per query head) the weight of a visible key
+// is sigmoid(s_j + gate_bias[h]), used as it is (nothing is normalised over the keys): o = sum_j w_j v_j.
 #include "api.h"
 #include "common.cuh"
 
@@ -35,6 +37,7 @@ struct AttnArgs {
   int window;
   float softcap;
   const float* sink;
+  const float* gate_bias;
 };
 
 template <typename T>
@@ -57,6 +60,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_simt_kernel(AttnArgs
 
   float m = -INFINITY, l = 0.0f;
   if (a.sink != nullptr) { m = a.sink[h]; l = 1.0f; }
+  const bool gated = a.gate_bias != nullptr;
+  const float gb = gated ? a.gate_bias[h] : 0.0f;
   float o[ATT_MAX_HD / 32];
 #pragma unroll
   for (int i = 0; i < ATT_MAX_HD / 32; ++i) o[i] = 0.0f;
@@ -72,13 +77,18 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_simt_kernel(AttnArgs
       s = dot * a.scale;
       if (a.softcap > 0.0f) s = a.softcap * tanhf(s / a.softcap);
     }
-    const float m_new = fmaxf(m, warp_max(s));
-    const float corr = expf(m - m_new);  // m = -inf on the first chunk: exp(-inf) = 0
-    const float pj = (j <= p) ? expf(s - m_new) : 0.0f;
-    l = l * corr + warp_sum(pj);
-    m = m_new;
+    float pj;
+    if (gated) {
+      pj = (j <= p) ? 1.0f / (1.0f + expf(-(s + gb))) : 0.0f;
+    } else {
+      const float m_new = fmaxf(m, warp_max(s));
+      const float corr = expf(m - m_new);  // m = -inf on the first chunk: exp(-inf) = 0
+      pj = (j <= p) ? expf(s - m_new) : 0.0f;
+      l = l * corr + warp_sum(pj);
+      m = m_new;
 #pragma unroll
-    for (int i = 0; i < ATT_MAX_HD / 32; ++i) o[i] *= corr;
+      for (int i = 0; i < ATT_MAX_HD / 32; ++i) o[i] *= corr;
+    }
     const int nk = (p - j0 + 1 < 32) ? p - j0 + 1 : 32;
     for (int k = 0; k < nk; ++k) {
       const float pk = __shfl_sync(0xffffffffu, pj, k);
@@ -92,7 +102,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_simt_kernel(AttnArgs
       }
     }
   }
-  const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+  const float inv = gated ? 1.0f : (l > 0.0f ? 1.0f / l : 0.0f);
   T* op = (T*)a.out + (size_t)t * a.ldo + (size_t)h * a.hd;
 #pragma unroll
   for (int i = 0; i < ATT_MAX_HD / 32; ++i) {
@@ -105,14 +115,15 @@ extern "C" int hb_attention_simt(int dtype, const void* q, int ldq, void* out, i
                                  const void* vcache, const int* tok_seq, const int* tok_pos,
                                  const int* seq_pages, int pages_stride, int n_tokens, int nh, int nkv,
                                  int hd, int page_size, float scale, int window, float softcap, const float* sink,
-                                 void* stream) {
+                                 const float* gate_bias, void* stream) {
   HB_REQUIRE(n_tokens > 0 && nh > 0 && nkv > 0 && hd > 0 && page_size > 0, "attention: sizes must be positive");
   HB_REQUIRE(nh % nkv == 0, "attention: %d query heads are not a multiple of %d key/value heads", nh, nkv);
   HB_REQUIRE(hd <= ATT_MAX_HD, "attention: head size %d exceeds the supported maximum %d", hd, ATT_MAX_HD);
   HB_REQUIRE(window >= 0, "attention: window must be >= 0");
   HB_REQUIRE(softcap >= 0.0f, "attention: the cap on the scores must be >= 0 (0: none)");
+  HB_REQUIRE(gate_bias == nullptr || sink == nullptr, "attention: sigmoid weights have no sink");
   AttnArgs a{q, ldq, out, ldo, kcache, vcache, tok_seq, tok_pos, seq_pages, pages_stride,
-             n_tokens, nh, nkv, hd, page_size, scale, window, softcap, sink};
+             n_tokens, nh, nkv, hd, page_size, scale, window, softcap, sink, gate_bias};
   const long long blocks = ceil_div_ll((long long)n_tokens * nh, ATT_WARPS);
   HB_REQUIRE(blocks < 2147483647LL, "attention: too many (token, head) pairs");
   if (dtype == HB_F32)

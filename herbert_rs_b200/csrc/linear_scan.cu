@@ -548,12 +548,13 @@ extern "C" int hb_linear_scan(int delta, const float* q, int ldq, const float* k
 }
 
 // ---------------------------------------------------------------------------------------------
-// y[t, u, :] = o / sqrt(mean(o^2) + eps) * w * act(gate): a unit u is one head (w [n] shared by the heads) or the whole
-// row of all heads (w [units * n] ... one unit).  act: 0 silu, 1 sigmoid.  One CTA per (token, unit).
+// y[t, u, :] = o / sqrt(mean(o^2) + eps) * w * act(gate): a unit u is one head (w [n] shared by the heads, or with
+// w_stride = n a weight [units * n] with a part for every head) or the whole row of all heads (one unit).
+// act: 0 silu, 1 sigmoid.  One CTA per (token, unit).
 template <typename T>
 __global__ void __launch_bounds__(256)
 gated_rmsnorm_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ w, float eps, const float* __restrict__ gate,
-                     int ldg, T* __restrict__ y, int ldy, int units, int n, int act) {
+                     int ldg, T* __restrict__ y, int ldy, int units, int n, int act, int w_stride) {
   __shared__ float red[32];
   pdl_wait();
   pdl_launch();
@@ -565,6 +566,7 @@ gated_rmsnorm_kernel(const float* __restrict__ o, int ldo, const float* __restri
   const float inv = 1.0f / sqrtf(ss / (float)n + eps);
   const float* g = gate + (size_t)t * ldg + (size_t)u * n;
   T* yr = y + (size_t)t * ldy + (size_t)u * n;
+  w += (size_t)u * w_stride;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const float gv = g[i];
     const float sg = 1.0f / (1.0f + expf(-gv));
@@ -573,18 +575,19 @@ gated_rmsnorm_kernel(const float* __restrict__ o, int ldo, const float* __restri
 }
 
 extern "C" int hb_gated_rmsnorm(int dtype, const float* o, int ldo, const float* w, float eps, const float* gate, int ldg,
-                                void* y, int ldy, int n_tokens, int units, int n, int act, void* stream) {
+                                void* y, int ldy, int n_tokens, int units, int n, int act, int w_stride, void* stream) {
   HB_REQUIRE(n_tokens > 0 && units > 0 && n > 0, "gated_rmsnorm: sizes must be positive");
   HB_REQUIRE(act == 0 || act == 1, "gated_rmsnorm: the gate's activation is 0 (silu) or 1 (sigmoid)");
+  HB_REQUIRE(w_stride == 0 || w_stride == n, "gated_rmsnorm: the weight is shared by the units (stride 0) or has a part for each (stride %d)", n);
   const long long blocks = (long long)n_tokens * units;
   HB_REQUIRE(blocks < 2147483647LL, "gated_rmsnorm: too many (token, unit) pairs");
   const int threads = n >= 1024 ? 256 : n >= 128 ? 128 : (n >= 64 ? 64 : 32);
   if (dtype == HB_F32)
     hb_launch(gated_rmsnorm_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream, o, ldo, w, eps, gate,
-              ldg, (float*)y, ldy, units, n, act);
+              ldg, (float*)y, ldy, units, n, act, w_stride);
   else
     hb_launch(gated_rmsnorm_kernel<bf16>, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream, o, ldo, w, eps, gate,
-              ldg, (bf16*)y, ldy, units, n, act);
+              ldg, (bf16*)y, ldy, units, n, act, w_stride);
   HB_CHECK_LAUNCH("gated_rmsnorm");
   return 0;
 }

@@ -158,6 +158,17 @@ extern "C" int hb_moe_route(int dtype, const void* h, int ld, const void* w_rout
   return 0;
 }
 
+// A gated expert's hidden value from its two products.  The clamped form (HB_ACT_SWISH_CLAMP, with a limit L):
+// g' = min(g, L), v' = clamp(v, -L, L), g' sigmoid(1.702 g') (v' + 1); every other activation: act(g) v.
+__device__ __forceinline__ float moe_act(float z, int act);
+__device__ __forceinline__ float moe_glu(float g, float v, int act, float limit) {
+  if (act == HB_ACT_SWISH_CLAMP) {
+    g = fminf(g, limit);
+    v = fminf(fmaxf(v, -limit), limit);
+    return (g / (1.0f + expf(-HB_SWISH_CLAMP_SLOPE * g))) * (v + 1.0f);
+  }
+  return moe_act(g, act) * v;
+}
 __device__ __forceinline__ float moe_act(float z, int act) {
   if (act == HB_ACT_GELU) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
   if (act == HB_ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
@@ -169,7 +180,7 @@ __device__ __forceinline__ float moe_act(float z, int act) {
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_up_kernel(const T* __restrict__ h, int ld, const T* __restrict__ up, const int* __restrict__ ids, T* __restrict__ mid,
-              int D, int F, int top, int act, int gated) {
+              int D, int F, int top, int act, int gated, float limit) {
   pdl_wait();
   pdl_launch();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -181,7 +192,7 @@ moe_up_kernel(const T* __restrict__ h, int ld, const T* __restrict__ up, const i
     const int grow = gated == 2 ? (f >> 3) * 16 + (f & 7) : f, urow = gated == 2 ? grow + 8 : F + f;
     const T* w = up + (size_t)e * 2 * F * D;
     const float g = warp_dot(hr, w + (size_t)grow * D, D, lane), v = warp_dot(hr, w + (size_t)urow * D, D, lane);
-    if (lane == 0) mid[(size_t)u * F + f] = from_f32<T>(moe_act(g, act) * v);
+    if (lane == 0) mid[(size_t)u * F + f] = from_f32<T>(moe_glu(g, v, act, limit));
     return;
   }
   const T* w = up + ((size_t)e * F + f) * D;
@@ -214,17 +225,18 @@ moe_down_kernel(const T* __restrict__ mid, const T* __restrict__ down, const int
 
 extern "C" int hb_moe_experts(int dtype, const void* h, int ld, const void* up, const void* down, const int* ids,
                               const float* weights, void* mid, float* y, int ldy, int n_tokens, int D, int F, int top,
-                              int act, int gated, int accumulate, void* stream) {
+                              int act, int gated, float act_limit, int accumulate, void* stream) {
   HB_REQUIRE(n_tokens > 0 && D > 0 && F > 0 && top > 0, "moe_experts: sizes must be positive");
+  HB_REQUIRE(act != HB_ACT_SWISH_CLAMP || gated, "moe_experts: the clamped activation is a gated expert's");
   HB_REQUIRE((long long)n_tokens * top < 2147483647LL && ceil_div(F, MOE_WARPS) <= 65535 && ceil_div(D, MOE_WARPS) <= 65535,
              "moe_experts: too many (token, choice) pairs or channels");
   cudaStream_t s = (cudaStream_t)stream;
   dim3 g1(n_tokens * top, ceil_div(F, MOE_WARPS)), g2(n_tokens, ceil_div(D, MOE_WARPS));
   if (dtype == HB_F32) {
-    hb_launch(moe_up_kernel<float>, g1, dim3(MOE_WARPS * 32), 0, s, (const float*)h, ld, (const float*)up, ids, (float*)mid, D, F, top, act, gated);
+    hb_launch(moe_up_kernel<float>, g1, dim3(MOE_WARPS * 32), 0, s, (const float*)h, ld, (const float*)up, ids, (float*)mid, D, F, top, act, gated, act_limit);
     hb_launch(moe_down_kernel<float>, g2, dim3(MOE_WARPS * 32), 0, s, (const float*)mid, (const float*)down, ids, weights, y, ldy, D, F, top, accumulate);
   } else {
-    hb_launch(moe_up_kernel<bf16>, g1, dim3(MOE_WARPS * 32), 0, s, (const bf16*)h, ld, (const bf16*)up, ids, (bf16*)mid, D, F, top, act, gated);
+    hb_launch(moe_up_kernel<bf16>, g1, dim3(MOE_WARPS * 32), 0, s, (const bf16*)h, ld, (const bf16*)up, ids, (bf16*)mid, D, F, top, act, gated, act_limit);
     hb_launch(moe_down_kernel<bf16>, g2, dim3(MOE_WARPS * 32), 0, s, (const bf16*)mid, (const bf16*)down, ids, weights, y, ldy, D, F, top, accumulate);
   }
   HB_CHECK_LAUNCH("moe_experts");
@@ -289,7 +301,7 @@ template <bool UP>
 __global__ void __launch_bounds__(MG_THREADS)
 moe_grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, void* __restrict__ C, int ldc,
                         const int* __restrict__ pair_off, const int* __restrict__ tile_off, const int* __restrict__ list, int E,
-                        int N, int K, int top, int act, int gated) {
+                        int N, int K, int top, int act, int gated, float limit) {
   __shared__ __align__(16) bf16 AW[2][(MG_TM + MG_TN) * (MG_TK + 8)];      // per buffer: the A tile, then the W tile
   __shared__ int rows[MG_TM];
   pdl_wait();
@@ -388,7 +400,7 @@ moe_grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restr
             const int n = n0 + wn + nt * 8 + 2 * t + c;      // a gate column; its up column is n + 8 (N is a multiple of 16)
             if (n >= N) continue;
             ((bf16*)C)[(size_t)pair * ldc + ((n0 + wn + nt * 8) >> 1) + 2 * t + c] =
-                __float2bfloat16_rn(moe_act(acc[m][nt][half * 2 + c], act) * acc[m][nt + 1][half * 2 + c]);
+                __float2bfloat16_rn(moe_glu(acc[m][nt][half * 2 + c], acc[m][nt + 1][half * 2 + c], act, limit));
           }
         continue;
       }
@@ -429,11 +441,12 @@ extern "C" long long hb_moe_grouped_scratch_ints(int n_tokens, int E, int top) {
 extern "C" int hb_moe_experts_grouped_bf16(const void* h, int ld, const void* up, const void* down, const int* ids,
                                            const float* weights, int* scratch, void* mid, float* part, float* y, int ldy,
                                            int n_tokens, int D, int E, int F, int top, int act, int gated,
-                                           int accumulate, void* stream) {
+                                           float act_limit, int accumulate, void* stream) {
   HB_REQUIRE(n_tokens > 0 && D > 0 && E > 0 && F > 0 && top > 0, "moe_experts_grouped: sizes must be positive");
   HB_REQUIRE(E <= MG_MAX_EXPERTS, "moe_experts_grouped: at most %d experts", MG_MAX_EXPERTS);
   HB_REQUIRE(D % 8 == 0 && F % 8 == 0 && ld % 8 == 0, "moe_experts_grouped: widths must be multiples of 8");
   HB_REQUIRE(gated == 0 || gated == 2, "moe_experts_grouped: gated experts need their gate and up rows in groups of 8");
+  HB_REQUIRE(act != HB_ACT_SWISH_CLAMP || gated, "moe_experts_grouped: the clamped activation is a gated expert's");
   HB_REQUIRE(n_tokens <= 65535, "moe_experts_grouped: at most 65535 tokens per call");
   const int n_pairs = n_tokens * top;
   int* pair_off = scratch;
@@ -444,9 +457,9 @@ extern "C" int hb_moe_experts_grouped_bf16(const void* h, int ld, const void* up
   const int max_tiles = ceil_div(n_pairs, MG_TM) + E;
   const int n_up = gated ? 2 * F : F;      // rows of an expert's first matrix
   hb_launch(moe_grouped_gemm_kernel<true>, dim3(max_tiles, ceil_div(n_up, MG_TN)), dim3(MG_THREADS), 0, s, (const bf16*)h, ld, (const bf16*)up,
-            mid, F, (const int*)pair_off, (const int*)tile_off, (const int*)list, E, n_up, D, top, act, gated);
+            mid, F, (const int*)pair_off, (const int*)tile_off, (const int*)list, E, n_up, D, top, act, gated, act_limit);
   hb_launch(moe_grouped_gemm_kernel<false>, dim3(max_tiles, ceil_div(D, MG_TN)), dim3(MG_THREADS), 0, s, (const bf16*)mid, F,
-            (const bf16*)down, (void*)part, D, (const int*)pair_off, (const int*)tile_off, (const int*)list, E, D, F, top, act, 0);
+            (const bf16*)down, (void*)part, D, (const int*)pair_off, (const int*)tile_off, (const int*)list, E, D, F, top, act, 0, 0.0f);
   hb_launch(moe_combine_kernel, dim3(ceil_div(D, 256), n_tokens), dim3(256), 0, s, (const float*)part, weights, y, ldy, D, top, accumulate, (const int*)nullptr);
   HB_CHECK_LAUNCH("moe_experts_grouped");
   return 0;

@@ -14,6 +14,8 @@
 //
 //   hb_rotate_heads_back    y[t, h, :dv] = a head's attention result turned by -p (pair m by -p * fv[m]), compacted
 //                           from heads of hd channels to heads of dv
+//   hb_head_gate            y[t, h, :dv] = a head's attention result times sigmoid(g[t, h]) (one number per token and
+//                           head), compacted likewise
 #include "api.h"
 #include "common.cuh"
 
@@ -104,7 +106,8 @@ extern "C" int hb_qkv_rotary_cache(int dtype, const float* rows, int ld, const f
   HB_REQUIRE(rot >= 0 && rot <= dk && rot % 2 == 0, "qkv_rotary_cache: %d rotated channels must be even and at most %d", rot, dk);
   HB_REQUIRE(rot == 0 || fqk != nullptr, "qkv_rotary_cache: rotated channels need their frequencies");
   HB_REQUIRE(fv == nullptr || dv % 2 == 0, "qkv_rotary_cache: rotated values need an even size, got %d", dv);
-  HB_REQUIRE(ld >= nh * dk + nkv * (dk + dv) && ldq >= nh * hd, "qkv_rotary_cache: rows are shorter than their heads");
+  // a step that stores nothing (it reads another layer's keys and values) brings rows of queries only
+  HB_REQUIRE(ld >= nh * dk + (write_cache ? nkv * (dk + dv) : 0) && ldq >= nh * hd, "qkv_rotary_cache: rows are shorter than their heads");
   RotPrepArgs a{rows, ld, wq, wk, eps, whole_norm, fqk, rot, halves, fv, tok_seq, tok_pos, seq_pages, pages_stride, q_out, ldq,
                 kcache, vcache, nh, nkv, dk, dv, hd, page_size, write_cache};
   if (dtype == HB_F32)
@@ -150,5 +153,35 @@ extern "C" int hb_rotate_heads_back(int dtype, const void* att, int ld, int hd, 
     hb_launch(rotate_heads_back_kernel<bf16>, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, (const bf16*)att, ld, hd, fv,
               halves, tok_pos, (bf16*)y, ldy, nh, dv);
   HB_CHECK_LAUNCH("rotate_heads_back");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_gate_kernel(const T* __restrict__ att, int ld, int hd, const float* __restrict__ gate, int ldg, T* __restrict__ y, int ldy,
+                 int nh, int dv) {
+  pdl_wait();
+  pdl_launch();
+  const int t = blockIdx.x;
+  const T* ar = att + (size_t)t * ld;
+  T* yr = y + (size_t)t * ldy;
+  for (int i = threadIdx.x; i < nh * dv; i += blockDim.x) {
+    const int h = i / dv, j = i - h * dv;
+    const float g = 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h]));
+    yr[i] = from_f32<T>(to_f32(ar[(size_t)h * hd + j]) * g);
+  }
+}
+
+extern "C" int hb_head_gate(int dtype, const void* att, int ld, int hd, const float* gate, int ldg, void* y, int ldy,
+                            int n_tokens, int nh, int dv, void* stream) {
+  HB_REQUIRE(n_tokens > 0 && nh > 0 && dv > 0 && hd >= dv, "head_gate: sizes must be positive and heads wide enough");
+  if (dtype == HB_F32)
+    hb_launch(head_gate_kernel<float>, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, (const float*)att, ld, hd, gate, ldg,
+              (float*)y, ldy, nh, dv);
+  else
+    hb_launch(head_gate_kernel<bf16>, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, (const bf16*)att, ld, hd, gate, ldg,
+              (bf16*)y, ldy, nh, dv);
+  HB_CHECK_LAUNCH("head_gate");
   return 0;
 }

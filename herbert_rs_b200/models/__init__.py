@@ -2,6 +2,7 @@
 
 from ..config.begupel import BegupelConfig
 from ..config.kebisun import KebisunConfig
+from ..config.nefivik import NefivikConfig
 from ..config.qwen3 import Qwen3Config
 from ..config.votapel import VotapelConfig
 from ..registry import register_architecture
@@ -19,5 +20,9 @@ register_architecture("Votapel", VotapelConfig)
 # values beside a gated delta rule; an input convolution per layer, RMS norms in groups on the sublayers'
 # results, a pair embedding, capped logits.
 register_architecture("Begupel", BegupelConfig)
+# Layers of sigmoid-weighted windowed attention (convolved projections, a gate per head, keys and values that a
+# later layer may read) and of a generalised delta rule, each sublayer between two norms and behind a gate; routed
+# experts in groups with a clamped activation; a second input by token id at every layer's end.
+register_architecture("Nefivik", NefivikConfig)
 
 __all__ = ["DecoderModel"]

@@ -12,7 +12,8 @@ earlier step instead of storing its own.
 
 Options of the spec: a scaled embedding, a learned vector per position, a second table chosen by (previous
 token, token) whose previous token is kept per sequence in the cache's fixed-size region (the first schedule
-step's entry carries it under the name "embedding.last_id"), a tanh cap on the logits.
+step's entry carries it under the name "embedding.last_id"), a tanh cap on the logits, a second table by token id
+of which blocks read their own columns (`ModelSpec.token_side_table`).
 """
 
 from __future__ import annotations
@@ -43,6 +44,7 @@ class DecoderModel:
         self.head = None
         self.position_table = None      # [max_position, hidden] learned vectors, if the spec names one
         self.pair_table = None          # [buckets + 1, hidden], if the spec has a pair embedding
+        self.token_side_table = None    # [vocab, columns], if blocks add a second input chosen by the token
         for i, st in enumerate(spec.schedule):
             if not (0 <= st.layer < len(self.blocks)):
                 raise ConfigError(f"schedule step {i} names layer {st.layer}, but there are {len(self.blocks)} layers")
@@ -60,6 +62,8 @@ class DecoderModel:
             out[s.position_table_name] = ParamSpec((rows, s.hidden_size), free_size=4096)
         if s.pair_embedding is not None:
             out[s.pair_embedding.table_name] = ParamSpec((s.pair_embedding.buckets + 1, s.hidden_size))
+        if s.token_side_table is not None:
+            out[s.token_side_table[0]] = ParamSpec((s.vocab_size, int(s.token_side_table[1])), init="wide")
         for i, b in enumerate(self.blocks):
             for name, ps in b.param_specs().items():
                 out[self.block_prefix(i) + name] = ps
@@ -87,6 +91,13 @@ class DecoderModel:
 
     def load_pair_table(self, t: torch.Tensor) -> None:
         self.pair_table = t.contiguous()
+
+    def load_token_side_table(self, t: torch.Tensor) -> None:
+        """One table for all layers; every block that adds a token's second input reads its own columns."""
+        self.token_side_table = t.contiguous()
+        for b in self.blocks:
+            if getattr(b, "load_token_table", None) is not None:
+                b.load_token_table(self.token_side_table)
 
     def longest_sequence(self) -> int:
         """The longest sequence the model can place: the spec's limit, and the position table's rows."""

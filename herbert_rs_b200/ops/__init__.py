@@ -18,8 +18,9 @@ from . import lib as _libmod
 from .options import KernelOptions
 
 F32, BF16 = 0, 1
-ACT_SILU, ACT_GELU_TANH, ACT_GELU, ACT_RELU = 0, 1, 2, 3
-ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "gelu": ACT_GELU, "relu": ACT_RELU}
+ACT_SILU, ACT_GELU_TANH, ACT_GELU, ACT_RELU, ACT_SWISH_CLAMP = 0, 1, 2, 3, 4
+# "swish_clamp" is a gated expert's: min(gate, L) sigmoid(1.702 min(gate, L)) (clamp(up, -L, L) + 1) with a limit L
+ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "gelu": ACT_GELU, "relu": ACT_RELU, "swish_clamp": ACT_SWISH_CLAMP}
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
 SKINNY_MAX_ROWS = 64
 # The one place where a choice between kernels can be changed (by a measurement script or a test
@@ -54,14 +55,16 @@ _SIGS = {
     "hb_gemm_stream_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                             ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p],
     "hb_attention_simt": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p],
+                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p],
     "hb_attention_decode_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p],
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p,
+                                 c_void_p],
     "hb_attention_decode_fused_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
                                        c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_attention_prefill_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p,
+                                  c_void_p],
     "hb_attention_prefill_tc_bf16": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p,
                                      c_void_p, c_void_p, c_void_p],
@@ -82,7 +85,7 @@ _SIGS = {
     "hb_latent_attention": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_moe_experts_grouped_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_moe_experts_tc_rows": [c_int, c_int, c_int],
     "hb_moe_experts_tc_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
@@ -97,7 +100,7 @@ _SIGS = {
     "hb_moe_route": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                      c_int, c_int, c_float, c_void_p],
     "hb_moe_experts": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                       c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_group_rmsnorm": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "hb_group_rmsnorm_residual": [c_int, c_void_p, c_int, c_void_p, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int, c_int, c_int, c_float, c_void_p],
@@ -114,12 +117,20 @@ _SIGS = {
     "hb_linear_scan": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_gated_rmsnorm": [c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                         c_int, c_void_p],
+                         c_int, c_int, c_void_p],
     "hb_qkv_rotary_cache": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_void_p, c_int, c_int, c_void_p,
                             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                             c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_rotate_heads_back": [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                              c_void_p],
+    "hb_head_gate": [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_general_delta_prepare": [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float,
+                                 c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_general_delta_scan": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                              c_int, c_void_p],
+    "hb_gated_norm_residual": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                               c_float, c_void_p, c_int, c_int, c_void_p],
+    "hb_token_gate": [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
 }
 _fns: dict = {}
 
@@ -610,12 +621,14 @@ def linear_scan(q, k, v, state, batch, out, heads, qk_heads, dk, dv, gates=None,
 
 def gated_rmsnorm(o, w, eps, gate, out, units, n, sigmoid_gate=False) -> None:
     """out[t, u, :] = o[t, u, :] / sqrt(mean(o[t, u, :]^2) + eps) * w * act(gate[t, u, :]) for `units` runs of n columns;
-    w [n] is shared by the units (units == 1: one norm over the whole row).  act: silu, or the sigmoid."""
+    w [n] is shared by the units (units == 1: one norm over the whole row), or w [units * n] has a part for each.
+    act: silu, or the sigmoid."""
     _check(o, torch.float32, "o"); _check(w, torch.float32, "w"); _check(gate, torch.float32, "gate"); _check(out, None, "out")
-    if w.numel() != n:
-        raise BackendError(f"gated_rmsnorm: the weight has {w.numel()} numbers, a unit {n}")
+    if w.numel() not in (n, units * n):
+        raise BackendError(f"gated_rmsnorm: the weight has {w.numel()} numbers, a unit {n}, all units {units * n}")
     _run("hb_gated_rmsnorm", dtype_code(out.dtype), o.data_ptr(), o.stride(0), w.data_ptr(), float(eps), gate.data_ptr(),
-         gate.stride(0), out.data_ptr(), out.stride(0), o.shape[0], int(units), int(n), 1 if sigmoid_gate else 0, _stream())
+         gate.stride(0), out.data_ptr(), out.stride(0), o.shape[0], int(units), int(n), 1 if sigmoid_gate else 0,
+         int(n) if (units > 1 and w.numel() == units * n) else 0, _stream())
 
 
 def qkv_rotary_cache(rows, wq, wk, eps, fqk, rot, halves, fv, batch, seq_pages, q_out, k_cache, v_cache, num_heads,
@@ -641,6 +654,64 @@ def rotate_heads_back(att, hd, fv, halves, tok_pos, out, num_heads, dv) -> None:
     _check(att, out.dtype, "att")
     _run("hb_rotate_heads_back", dtype_code(out.dtype), att.data_ptr(), att.stride(0), int(hd), _ptr(fv), 1 if halves else 0,
          tok_pos.data_ptr(), out.data_ptr(), out.stride(0), att.shape[0], int(num_heads), int(dv), _stream())
+
+
+def head_gate(att, hd, gate, out, num_heads, dv) -> None:
+    """out[t, h, :dv] = the first dv channels of head h of att (heads of hd channels) times sigmoid(gate[t, h]);
+    gate float [T, num_heads] (rows may be strided)."""
+    _check(att, out.dtype, "att"); _check(gate, torch.float32, "gate")
+    _run("hb_head_gate", dtype_code(out.dtype), att.data_ptr(), att.stride(0), int(hd), gate.data_ptr(), gate.stride(0),
+         out.data_ptr(), out.stride(0), att.shape[0], int(num_heads), int(dv), _stream())
+
+
+def general_delta_prepare(rows, r_off, k_off, a_off, low_off, w2, w0, a0, decay_c, unit_eps, prep, heads, dk) -> None:
+    """From float rows of a projection (column ranges r, k, a of heads * dk numbers from their offsets, the decay's
+    inner row of w2.shape[1] numbers from low_off): prep [T, heads, 5, dk] float = r, k, w, u, a * u with
+    u = k / sqrt(sum k^2 + unit_eps) per head, w = exp(-decay_c * sigmoid(w2 tanh(low) + w0)), a = sigmoid(a + a0)."""
+    _check(rows, torch.float32, "rows"); _check(w2, None, "w2"); _check(w0, torch.float32, "w0"); _check(a0, torch.float32, "a0")
+    _check(prep, torch.float32, "prep")
+    if not (w2.is_contiguous() and prep.is_contiguous()) or tuple(w2.shape[:1]) != (heads * dk,):
+        raise BackendError("general_delta_prepare: w2 must be [heads * dk, rank] and contiguous, prep contiguous")
+    _run("hb_general_delta_prepare", dtype_code(w2.dtype), rows.data_ptr(), rows.stride(0), int(r_off), int(k_off), int(a_off),
+         int(low_off), w2.data_ptr(), w0.data_ptr(), a0.data_ptr(), float(decay_c), float(unit_eps), prep.data_ptr(),
+         rows.shape[0], int(heads), int(dk), w2.shape[1], _stream())
+
+
+def general_delta_scan(prep, v, state, batch, out, heads, dk, dv) -> None:
+    """The generalised delta rule over every sequence's tokens of the step, in order, from and into state[slot]
+    ([slots, heads, dk, dv] float): S <- diag(w) S - (a u) (u^T S) + k v^T (both terms read the old S); o = S^T r.
+    prep [T, heads, 5, dk] as `general_delta_prepare` leaves it; v and out [T, heads dv] float column ranges of rows."""
+    for t, n in ((prep, "prep"), (v, "v"), (state, "state"), (out, "out")):
+        _check(t, torch.float32, n)
+    if not state.is_contiguous() or tuple(state.shape[1:]) != (heads, dk, dv):
+        raise BackendError(f"general_delta_scan: state of shape {tuple(state.shape)} is not [slots, {heads}, {dk}, {dv}]")
+    _run("hb_general_delta_scan", prep.data_ptr(), v.data_ptr(), v.stride(0), state.data_ptr(), batch.seq_slot.data_ptr(),
+         batch.seq_start.data_ptr(), out.data_ptr(), out.stride(0), batch.n_seqs, int(heads), int(dk), int(dv), _stream())
+
+
+def gated_norm_residual(y, w, eps, x, dtype, gate=None, gate_bias=None, next_norm=None, h=None) -> None:
+    """x += v / sqrt(mean(v^2) + eps) * w with v = y * sigmoid(gate + gate_bias) (gate None: v = y); all float.
+    h, if given, receives in the activation dtype `dtype` the updated x, or with next_norm = (w2, eps2) its RMS norm
+    x / sqrt(mean(x^2) + eps2) * w2."""
+    _check(y, torch.float32, "y"); _check(w, torch.float32, "w"); _check(x, torch.float32, "x")
+    if gate is not None:
+        _check(gate, torch.float32, "gate")
+    if gate_bias is not None:
+        _check(gate_bias, torch.float32, "gate_bias")
+    if h is not None:
+        _check(h, dtype, "h")
+    if not x.is_contiguous() or (h is not None and not h.is_contiguous()):
+        raise BackendError("gated_norm_residual: x and h must be contiguous")
+    w2, eps2 = next_norm if next_norm is not None else (None, 0.0)
+    _run("hb_gated_norm_residual", dtype_code(dtype), y.data_ptr(), y.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0,
+         _ptr(gate_bias), w.data_ptr(), float(eps), x.data_ptr(), _ptr(w2), float(eps2), _ptr(h), x.shape[0], x.shape[1], _stream())
+
+
+def token_gate(s, table, col0, ids, out) -> None:
+    """out[t, j] = gelu_tanh(s[t, j]) * table[ids[t], col0 + j]; s float [T, m], table in out's dtype."""
+    _check(s, torch.float32, "s"); _check(table, out.dtype, "table"); _check(ids, torch.int32, "ids")
+    _run("hb_token_gate", dtype_code(out.dtype), s.data_ptr(), s.stride(0), table.data_ptr(), table.stride(0), int(col0),
+         ids.data_ptr(), out.data_ptr(), out.stride(0), s.shape[0], s.shape[1], table.shape[0], _stream())
 
 
 def moe_route(h, w_router, ids, weights, top, renorm=False, score=0, groups=1, keep=1, group_top=2, weight_scale=1.0) -> None:
@@ -700,7 +771,7 @@ def moe_experts_tc(h, up, down, ids, weights, y, accumulate, scratch) -> None:
          1 if accumulate else 0, _error_flag(y.device).data_ptr(), _stream())
 
 
-def moe_experts_grouped(h, up, down, ids, weights, y, act, accumulate, scratch, gated=0) -> None:
+def moe_experts_grouped(h, up, down, ids, weights, y, act, accumulate, scratch, gated=0, act_limit=0.0) -> None:
     """moe_experts for many tokens: pairs grouped by expert on the device, tiles of 64 pairs on the tensor cores."""
     _check(h, torch.bfloat16, "h"); _check(up, torch.bfloat16, "up"); _check(down, torch.bfloat16, "down"); _check(y, torch.float32, "y")
     T, top = ids.shape
@@ -712,20 +783,20 @@ def moe_experts_grouped(h, up, down, ids, weights, y, act, accumulate, scratch, 
     part = scratch((T * top, D), torch.float32)
     _run("hb_moe_experts_grouped_bf16", h.data_ptr(), h.stride(0), up.data_ptr(), down.data_ptr(), ids.data_ptr(), weights.data_ptr(),
          ints.data_ptr(), mid.data_ptr(), part.data_ptr(), y.data_ptr(), y.stride(0), T, D, E, F, top, int(act),
-         int(gated), 1 if accumulate else 0, _stream())
+         int(gated), float(act_limit), 1 if accumulate else 0, _stream())
 
 
-def moe_experts(h, up, down, ids, weights, mid, y, act, accumulate=False, gated=0) -> None:
+def moe_experts(h, up, down, ids, weights, mid, y, act, accumulate=False, gated=0, act_limit=0.0) -> None:
     """y[t] (+)= sum_r weights[t, r] * down[e] act(up[e] h[t]), e = ids[t, r]; up [E, F, D], down [E, D, F] in
     h's dtype; mid [T * top, F] scratch in h's dtype; y float.  gated: up is [E, 2F, D] and an expert is
     down[e] (act(gate h) * (up h)), with the gate and up rows in turn in groups of 8 (GATED_GROUPS_OF_8) or all
-    gate rows before all up rows (GATED_HALVES)."""
+    gate rows before all up rows (GATED_HALVES).  act ACT_SWISH_CLAMP (gated experts only) takes `act_limit`."""
     _check(h, None, "h"); _check(up, h.dtype, "up"); _check(down, h.dtype, "down"); _check(mid, h.dtype, "mid"); _check(y, torch.float32, "y")
     if not (up.is_contiguous() and down.is_contiguous() and mid.is_contiguous()):
         raise BackendError("moe_experts: up, down and mid must be contiguous")
     _run("hb_moe_experts", dtype_code(h.dtype), h.data_ptr(), h.stride(0), up.data_ptr(), down.data_ptr(), ids.data_ptr(),
          weights.data_ptr(), mid.data_ptr(), y.data_ptr(), y.stride(0), h.shape[0], h.shape[1], down.shape[2], ids.shape[1],
-         int(act), int(gated), 1 if accumulate else 0, _stream())
+         int(act), int(gated), float(act_limit), 1 if accumulate else 0, _stream())
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> None:
@@ -769,15 +840,18 @@ def gemm_simt(a, w, c, epilogue=EPI_STORE) -> None:
 
 
 def attention_simt(q, ldq, out, k_cache, v_cache, tok_seq, tok_pos, seq_pages, num_heads, num_kv_heads,
-                   head_dim, page_size, scale, window, softcap=None, sink=None) -> None:
+                   head_dim, page_size, scale, window, softcap=None, sink=None, gate_bias=None) -> None:
     """Any shape, both precisions.  softcap c: score <- c * tanh(score / c); sink [num_heads] float: exp(sink)
-    joins each head's softmax denominator.  v_cache may be k_cache (values that are the keys)."""
+    joins each head's softmax denominator.  v_cache may be k_cache (values that are the keys).  gate_bias
+    [num_heads] float: no softmax, a visible key weighs sigmoid(score + gate_bias[head]) as it is."""
     if sink is not None:
         _check(sink, torch.float32, "sink")
+    if gate_bias is not None:
+        _check(gate_bias, torch.float32, "gate_bias")
     _run("hb_attention_simt", dtype_code(out.dtype), q.data_ptr(), int(ldq), out.data_ptr(), out.stride(0),
          k_cache.data_ptr(), v_cache.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_pages.data_ptr(),
          seq_pages.stride(0), out.shape[0], num_heads, num_kv_heads, head_dim, page_size, float(scale),
-         int(window or 0), float(softcap or 0.0), _ptr(sink), _stream())
+         int(window or 0), float(softcap or 0.0), _ptr(sink), _ptr(gate_bias), _stream())
 
 
 _argmax_scratch: dict = {}
@@ -1135,11 +1209,13 @@ def decode_splits(n_seqs: int, num_kv_heads: int, max_tiles: int, device=None) -
 
 
 def attention_decode(q, ldq, out, k_cache, v_cache, seq_len, seq_pages, scratch, num_heads, num_kv_heads,
-                     head_dim, page_size, nsplit, scale, window, softcap=None, sink=None) -> None:
+                     head_dim, page_size, nsplit, scale, window, softcap=None, sink=None, gate_bias=None) -> None:
     """One query per sequence (row b of q) over the cache; scratch holds the splits' partial results.
-    softcap and sink as in `attention`; the sink joins the denominator where the splits are combined."""
+    softcap, sink and gate_bias as in `attention`; the sink joins the denominator where the splits are combined."""
     if sink is not None:
         _check(sink, torch.float32, "sink")
+    if gate_bias is not None:
+        _check(gate_bias, torch.float32, "gate_bias")
     _check(out, torch.bfloat16, "out"); _check(scratch, torch.float32, "scratch")
     n = out.shape[0]
     if scratch.numel() < attention_decode_scratch_floats(n, num_heads, head_dim, nsplit):
@@ -1147,7 +1223,7 @@ def attention_decode(q, ldq, out, k_cache, v_cache, seq_len, seq_pages, scratch,
     _run("hb_attention_decode_bf16", q.data_ptr(), int(ldq), out.data_ptr(), out.stride(0), k_cache.data_ptr(),
          v_cache.data_ptr(), seq_len.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0), scratch.data_ptr(),
          n, num_heads, num_kv_heads, head_dim, page_size, int(nsplit), float(scale), int(window or 0),
-         float(softcap or 0.0), _ptr(sink), _stream())
+         float(softcap or 0.0), _ptr(sink), _ptr(gate_bias), _stream())
 
 
 _DECODE_COUNTERS = 65536
@@ -1180,15 +1256,18 @@ def attention_decode_fused(qkv, out, k_cache, v_cache, q_weight, k_weight, eps, 
 
 
 def attention_prefill(q, ldq, out, k_cache, v_cache, seq_start, seq_pos0, seq_pages, n_seqs, max_q_len,
-                      num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap=None, sink=None) -> None:
+                      num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap=None, sink=None,
+                      gate_bias=None) -> None:
     """Causal attention of packed query rows (seq_start marks the sequences) over the cache."""
     _check(out, torch.bfloat16, "out")
     if sink is not None:
         _check(sink, torch.float32, "sink")
+    if gate_bias is not None:
+        _check(gate_bias, torch.float32, "gate_bias")
     _run("hb_attention_prefill_bf16", q.data_ptr(), int(ldq), out.data_ptr(), out.stride(0), k_cache.data_ptr(),
          v_cache.data_ptr(), seq_start.data_ptr(), seq_pos0.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0),
          int(n_seqs), int(max_q_len), num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
-         float(softcap or 0.0), _ptr(sink), _stream())
+         float(softcap or 0.0), _ptr(sink), _ptr(gate_bias), _stream())
 
 
 def attention_prefill_tc(q, ldq, out, k_cache, v_cache, seq_start, seq_pos0, seq_pages, n_seqs, max_q_len,
@@ -1231,31 +1310,32 @@ def _decode_kernel_ok(out, num_heads, num_kv_heads, head_dim, page_size) -> bool
 
 
 def attention(q, ldq, out, k_cache, v_cache, batch, num_heads, num_kv_heads, head_dim, page_size,
-              scale, window, seq_pages, scratch=None, softcap=None, sink=None) -> None:
+              scale, window, seq_pages, scratch=None, softcap=None, sink=None, gate_bias=None) -> None:
     """Attention of every token of the step over its sequence's cached keys and values.
 
     bfloat16 steps of one token per sequence take the split-key tensor-core kernel, other bfloat16
     steps the flash kernel; head sizes or pages those cannot serve, and the float32 path, take
     the any-shape kernel.  Every kernel takes a cap on the scores (softcap c: s <- c * tanh(s / c)) and a sink
-    (a float per query head whose exponential joins the softmax's denominator); v_cache may be k_cache."""
+    (a float per query head whose exponential joins the softmax's denominator); v_cache may be k_cache.  With
+    `gate_bias` (a float per query head) there is no softmax: a visible key weighs sigmoid(score + gate_bias[head])."""
     if options.attention == "simt":
         attention_simt(q, ldq, out, k_cache, v_cache, batch.tok_seq, batch.tok_pos, seq_pages, num_heads,
-                       num_kv_heads, head_dim, page_size, scale, window, softcap, sink)
+                       num_kv_heads, head_dim, page_size, scale, window, softcap, sink, gate_bias)
         return
     if batch.is_decode and scratch is not None and _decode_kernel_ok(out, num_heads, num_kv_heads, head_dim, page_size):
         tiles = seq_pages.shape[1] * (page_size // 64)
         nsplit = decode_splits(batch.n_seqs, num_kv_heads, tiles)
         buf = scratch((attention_decode_scratch_floats(batch.n_seqs, num_heads, head_dim, nsplit),), torch.float32)
         attention_decode(q, ldq, out, k_cache, v_cache, batch.seq_len, seq_pages, buf, num_heads, num_kv_heads,
-                         head_dim, page_size, nsplit, scale, window, softcap, sink)
+                         head_dim, page_size, nsplit, scale, window, softcap, sink, gate_bias)
         return
-    if _prefill_tc_ok(q, ldq, out, head_dim, page_size):
+    if gate_bias is None and _prefill_tc_ok(q, ldq, out, head_dim, page_size):
         attention_prefill_tc(q, ldq, out, k_cache, v_cache, batch.seq_start, batch.seq_pos0, seq_pages, batch.n_seqs,
                              batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap, sink)
         return
     if _prefill_kernel_ok(out, head_dim, page_size):
         attention_prefill(q, ldq, out, k_cache, v_cache, batch.seq_start, batch.seq_pos0, seq_pages, batch.n_seqs,
-                          batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap, sink)
+                          batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap, sink, gate_bias)
         return
     attention_simt(q, ldq, out, k_cache, v_cache, batch.tok_seq, batch.tok_pos, seq_pages, num_heads,
-                   num_kv_heads, head_dim, page_size, scale, window, softcap, sink)
+                   num_kv_heads, head_dim, page_size, scale, window, softcap, sink, gate_bias)

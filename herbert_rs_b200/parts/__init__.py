@@ -8,13 +8,14 @@ from .latent_attention import LatentAttentionMixer
 from .gla import GatedLinearAttentionMixer
 from .lightning import LightningMixer
 from .gated_delta import GatedDeltaMixer
+from .general_delta import GeneralDeltaMixer
 from .side_by_side import SideBySideMixer
 from .swiglu import SwiGLU, join_gate_up
 from .moe import RoutedFeedForward
-from .block import ParallelBlock, PreNormBlock, SublayerNormBlock
+from .block import ParallelBlock, PreNormBlock, SandwichBlock, SublayerNormBlock
 
 __all__ = ["Block", "FeedForward", "Mixer", "Norm", "ParamSpec", "Part", "RMSNorm", "RotaryEncoding",
            "rope_tables", "AttentionMixer", "SwiGLU", "join_gate_up", "PreNormBlock", "LayerNorm", "ScaledRotary",
            "scaled_frequencies", "LatentAttentionMixer", "GatedLinearAttentionMixer", "RoutedFeedForward",
            "SublayerNormBlock", "ParallelBlock", "RotaryPairs", "pair_frequencies", "LightningMixer", "GatedDeltaMixer",
-           "SideBySideMixer"]
+           "SideBySideMixer", "GeneralDeltaMixer", "SandwichBlock"]

@@ -23,6 +23,11 @@ every q and k head are turned at the token's position, and the values are stored
 position over all their channels; a head's result is turned back by the query's position, so that it depends
 on the distance only.  Values may be narrower or wider than keys: the cache's heads have max(dk, dv)
 channels, the unused ones are zeros, and the attention kernels run unchanged over heads of that size.
+The same form takes four more options: a short causal convolution over time on every channel of q, k and v right
+after the projection (its last inputs are state of the sequence); sigmoid weights, sigmoid(score + b_head) for
+every visible key with nothing normalised over the keys; one output gate per token and head, sigmoid(G h), whose
+rows are part of the one projection; and a mixer without keys and values of its own, whose schedule step reads
+another step's cache with its own queries, window and gates.
 """
 
 from __future__ import annotations
@@ -30,7 +35,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from ..cache import CacheNeed, KVNeed
+from ..cache import CacheNeed, KVNeed, StateNeed
 from ..errors import ConfigError
 from ..registry import build_part, register_part
 from .base import Mixer, ParamSpec
@@ -49,7 +54,8 @@ class AttentionMixer(Mixer):
         # the plain form (no option set) keeps the path with the fused kernels of the dense decoder
         self.plain = not (spec.bias or spec.values_are_keys or spec.q_temperature or spec.softcap or spec.sink)
         self.pairs = bool(spec.whole_qk_norm or spec.value_dim is not None or spec.value_rotation is not None
-                          or getattr(spec.position, "kind", None) == "rope_pairs")
+                          or getattr(spec.position, "kind", None) == "rope_pairs" or spec.key_weights != "softmax"
+                          or spec.conv_taps is not None or spec.head_gate or spec.reads_kv)
         if self.pairs:
             self._init_pairs()
             return
@@ -79,7 +85,17 @@ class AttentionMixer(Mixer):
         self.dv = s.value_dim if s.value_dim is not None else s.head_dim
         self.hd = max(self.dk, self.dv)              # the cache's and the attention kernels' head size
         self.q_dim, self.kv_dim = self.nh * self.dk, self.nkv * self.dk
-        self.qkv_dim = self.q_dim + self.kv_dim + self.nkv * self.dv
+        if s.key_weights not in ("softmax", "sigmoid"):
+            raise ConfigError(f"unknown key weights {s.key_weights!r}: softmax, sigmoid")
+        self.sigmoid_keys = s.key_weights == "sigmoid"
+        self.reads_kv = bool(s.reads_kv)
+        self.taps = int(s.conv_taps) if s.conv_taps is not None else 0
+        if s.conv_taps is not None and self.taps < 1:
+            raise ConfigError("a convolution has at least one tap")
+        # what the projection's rows hold: q, then (unless another step's are read) k and v, then one gate per head
+        self.qkv_dim = self.q_dim + (0 if self.reads_kv else self.kv_dim + self.nkv * self.dv)
+        self.proj_dim = self.qkv_dim + (self.nh if s.head_gate else 0)
+        self.key_bias = self.w_conv = None
         self.value_position = build_part("position", s.value_rotation, rt=self.rt) if s.value_rotation is not None else None
         if self.value_position is not None and self.value_position.rotary_dim != self.dv:
             raise ConfigError(f"values of {self.dv} channels are turned over all of them, not {self.value_position.rotary_dim}")
@@ -89,14 +105,24 @@ class AttentionMixer(Mixer):
         self.can_store = True
         self.shared_values = False
 
+    def _projections(self):
+        """(tensor name, rows) of the projections that pass the convolution, in the order of the rows."""
+        out = [(self.n_q, self.q_dim)]
+        if not self.reads_kv:
+            out += [(self.n_k, self.kv_dim), (self.n_v, self.nkv * self.dv)]
+        return out
+
     def _param_specs_pairs(self):
         s = self.spec
-        p = {
-            self.n_q: ParamSpec((self.q_dim, s.hidden_size)),
-            self.n_k: ParamSpec((self.kv_dim, s.hidden_size)),
-            self.n_v: ParamSpec((self.nkv * self.dv, s.hidden_size)),
-            self.n_o: ParamSpec((s.hidden_size, self.nh * self.dv)),
-        }
+        p = {n: ParamSpec((rows, s.hidden_size)) for n, rows in self._projections()}
+        p[self.n_o] = ParamSpec((s.hidden_size, self.nh * self.dv))
+        if self.taps:
+            for n, rows in self._projections():
+                p[n + s.conv_suffix] = ParamSpec((rows, self.taps), role="vector", init="wide")
+        if self.sigmoid_keys:
+            p[s.key_bias_name] = ParamSpec((self.nh,), role="vector", init="wide")
+        if s.head_gate:
+            p[s.head_gate_name] = ParamSpec((self.nh, s.hidden_size))
         if s.whole_qk_norm:
             p[s.norm_names[0]] = ParamSpec((self.q_dim,), role="vector", init="ones_noise")
             p[s.norm_names[1]] = ParamSpec((self.kv_dim,), role="vector", init="ones_noise")
@@ -104,16 +130,25 @@ class AttentionMixer(Mixer):
 
     def _load_pairs(self, tensors):
         s = self.spec
-        self.wqkv = torch.cat([tensors[self.n_q], tensors[self.n_k], tensors[self.n_v]], dim=0).contiguous()
+        mats = [tensors[n] for n, _ in self._projections()] + ([tensors[s.head_gate_name]] if s.head_gate else [])
+        self.wqkv = torch.cat(mats, dim=0).contiguous()
         self.wo = tensors[self.n_o].contiguous()
+        if self.taps:
+            self.w_conv = torch.cat([tensors[n + s.conv_suffix] for n, _ in self._projections()], dim=0).contiguous()
+        if self.sigmoid_keys:
+            self.key_bias = tensors[s.key_bias_name].contiguous()
         if s.whole_qk_norm:
             self.q_norm = tensors[s.norm_names[0]].contiguous()
             self.k_norm = tensors[s.norm_names[1]].contiguous()
 
     def _forward_pairs(self, h, residual, batch, cache, accumulate):
         s, ws, T = self.spec, self.rt.workspace, h.shape[0]
-        rows = ws.take((T, self.qkv_dim), torch.float32)
-        ops.gemm(h, self.wqkv, rows, ops.EPI_STORE_F32, scratch=ws.take)
+        proj = ws.take((T, self.proj_dim), torch.float32)
+        ops.gemm(h, self.wqkv, proj, ops.EPI_STORE_F32, scratch=ws.take)
+        rows = proj
+        if self.taps:
+            rows = ws.take((T, self.qkv_dim), torch.float32)
+            ops.short_conv(proj[:, :self.qkv_dim], self.w_conv, cache.states.get("conv"), batch, rows)
         q = ws.take((T, self.nh * self.hd), h.dtype)
         pages = batch.pages[cache.kv_group]
         pos, vpos = self.position, self.value_position
@@ -122,15 +157,18 @@ class AttentionMixer(Mixer):
         ops.qkv_rotary_cache(rows, self.q_norm, self.k_norm, s.qk_norm.eps if s.qk_norm is not None else 0.0,
                              pos.freq if pos is not None else None, pos.rotary_dim if pos is not None else 0, halves, fv,
                              batch, pages, q, cache.k, cache.v, self.nh, self.nkv, self.dk, self.dv, self.hd,
-                             cache.page_size, write_cache=cache.writes_kv)
+                             cache.page_size, write_cache=cache.writes_kv and not self.reads_kv)
         att = ws.take((T, self.nh * self.hd), h.dtype)
         ops.attention(q, q.stride(0), att, cache.k, cache.v, batch, self.nh, self.nkv, self.hd, cache.page_size, s.scale,
-                      s.window, pages, scratch=ws.take)
-        if fv is not None or self.hd != self.dv:
-            y = ws.take((T, self.nh * self.dv), h.dtype)
+                      s.window, pages, scratch=ws.take, gate_bias=self.key_bias)
+        y, hd = att, self.hd
+        if fv is not None or (self.hd != self.dv and not s.head_gate):
+            y, hd = ws.take((T, self.nh * self.dv), h.dtype), self.dv
             ops.rotate_heads_back(att, self.hd, fv, halves, batch.tok_pos, y, self.nh, self.dv)
-        else:
-            y = att
+        if s.head_gate:
+            gated = ws.take((T, self.nh * self.dv), h.dtype)
+            ops.head_gate(y, hd, proj[:, self.qkv_dim:], gated, self.nh, self.dv)
+            y = gated
         ops.gemm(y, self.wo, residual, ops.EPI_RESIDUAL if accumulate else ops.EPI_STORE_F32, scratch=ws.take)
 
     def param_specs(self):
@@ -172,7 +210,12 @@ class AttentionMixer(Mixer):
         return (self.wqkv.numel() + self.wo.numel()) * self.wqkv.element_size()
 
     def cache_need(self):
-        return CacheNeed(kv=KVNeed(self.nkv, self.hd, self.spec.window, planes=1 if self.shared_values else 2))
+        s = self.spec
+        keep = s.window if s.cache_window == -1 else s.cache_window
+        states = ()
+        if self.pairs and self.taps > 1:
+            states = (("conv", StateNeed((self.taps - 1, self.qkv_dim), torch.float32)),)
+        return CacheNeed(kv=KVNeed(self.nkv, self.hd, keep, planes=1 if self.shared_values else 2), states=states)
 
     def _forward_options(self, h, residual, batch, cache, accumulate):
         """The path of a mixer with any of the spec's options (see the module's notes)."""

@@ -274,6 +274,155 @@ class ParallelBlock(Block):
         return h_next
 
 
+class SandwichBlock(Block):
+    """A norm before and after each sublayer, and a gate on each result:
+
+        h = norm1(x);  x += post1( mixer(h) * sigmoid(R1 h + b1) )
+        h = norm2(x);  x += post2( ffn(h)   * sigmoid(R2 h + b2) )
+        e = table[token][column0 : column0 + m];  y = P (gelu_tanh(G x) * e);  x += y / sqrt(mean(y^2) + eps) * w
+
+    The gates are optional (`BlockSpec.residual_gates`), so are the feed-forward and the last line (`token_side`: a
+    second input that the token's id chooses from a table of the model's, this layer its own columns of it).
+    A sublayer stores its result as floats; gate, norm of the result, the sum and the norm that the next sublayer (or
+    the next block) begins with are one kernel, so that between two sublayers the stream is read and written once."""
+
+    chains_norms = True
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        self.norm1 = build_part("norm", spec.norm1, rt=rt)
+        self.mixer = build_part("mixer", spec.mixer, rt=rt)
+        self.ffn = build_part("ffn", spec.ffn, rt=rt) if spec.ffn is not None else None
+        self.norm2 = build_part("norm", spec.norm2, rt=rt) if self.ffn is not None else None
+        if not spec.post_norms or len(spec.post_norms) != 2:
+            raise ConfigError("a block with a norm before and after each sublayer needs the two norms of the results")
+        self.post1 = build_part("norm", spec.post_norms[0], rt=rt)
+        self.post2 = build_part("norm", spec.post_norms[1], rt=rt) if self.ffn is not None else None
+        for norm in (self.norm1, self.norm2, self.post1, self.post2):
+            if norm is not None and norm.shareable() is None:
+                raise ConfigError("the block with a norm before and after each sublayer applies plain RMS norms")
+        for part in (self.mixer, self.ffn):
+            if part is not None and not part.can_store:
+                raise ConfigError(f"{type(part).__name__} cannot store its result apart from the residual stream, "
+                                  "which a block that norms a sublayer's result needs")
+        self._names = dict(spec.names)
+        self.gate_names = tuple(spec.residual_gates) if spec.residual_gates else None
+        self.gate_bias_suffix = spec.residual_gate_bias
+        self.side = spec.token_side
+        self.gate1 = self.gate2 = self.gate1_b = self.gate2_b = None
+        self.side_gate = self.side_proj = self.side_norm = self.side_table = None
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for _, p in self.children())
+
+    def children(self):
+        parts = [("norm1", self.norm1), ("mixer", self.mixer), ("post1", self.post1)]
+        if self.ffn is not None:
+            parts += [("norm2", self.norm2), ("ffn", self.ffn), ("post2", self.post2)]
+        return tuple(parts)
+
+    def _key(self, local, name):
+        prefix = self._names[local]
+        return f"{prefix}.{name}" if prefix else name
+
+    def param_specs(self):
+        out = {}
+        for local, part in self.children():
+            for name, ps in part.param_specs().items():
+                out[self._key(local, name)] = ps
+        D = self.spec.norm1.dim
+        if self.gate_names:
+            for n in self.gate_names[:2 if self.ffn is not None else 1]:
+                out[n] = ParamSpec((D, D))
+                out[n + self.gate_bias_suffix] = ParamSpec((D,), role="vector", init="wide")
+        if self.side is not None:
+            g, p, w = self.side.names
+            out[g] = ParamSpec((self.side.dim, D))
+            out[p] = ParamSpec((D, self.side.dim), init="wide")
+            out[w] = ParamSpec((D,), role="vector", init="ones_noise")
+        return out
+
+    def load(self, tensors):
+        for local, part in self.children():
+            part.load({name: tensors[self._key(local, name)] for name in part.param_specs()})
+        if self.gate_names:
+            self.gate1 = tensors[self.gate_names[0]].contiguous()
+            self.gate1_b = tensors[self.gate_names[0] + self.gate_bias_suffix].contiguous()
+            if self.ffn is not None:
+                self.gate2 = tensors[self.gate_names[1]].contiguous()
+                self.gate2_b = tensors[self.gate_names[1] + self.gate_bias_suffix].contiguous()
+        if self.side is not None:
+            g, p, w = self.side.names
+            self.side_gate, self.side_proj, self.side_norm = tensors[g].contiguous(), tensors[p].contiguous(), tensors[w].contiguous()
+
+    def load_token_table(self, table):
+        """The model's second table [vocab, columns]; this block reads `token_side.dim` columns from `column0`."""
+        self.side_table = table
+
+    def weight_bytes(self):
+        n = sum(p.weight_bytes() for _, p in self.children())
+        for w in (self.gate1, self.gate2, self.side_gate, self.side_proj):
+            if w is not None:
+                n += w.numel() * w.element_size()
+        return n
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def first_norm(self):
+        return self.norm1
+
+    def _join(self, y, h_in, gate_w, gate_b, post, x, next_norm, want_h):
+        """x += post(y * sigmoid(gate_w h_in + gate_b)); returns what the next sublayer reads (its norm of x, or x
+        itself in the activation dtype where `next_norm` is None), or None if nothing is wanted."""
+        ws, dtype = self.rt.workspace, self.rt.dtype
+        z = None
+        if gate_w is not None:
+            z = ws.take(x.shape, torch.float32)
+            ops.gemm(h_in, gate_w, z, ops.EPI_STORE_F32, scratch=ws.take)
+        h = ws.take(x.shape, dtype) if want_h else None
+        ops.gated_norm_residual(y, post.weight, post.eps, x, dtype, gate=z, gate_bias=gate_b, next_norm=next_norm, h=h)
+        return h
+
+    def forward(self, x, batch, cache, normed=None, next_norm=None):
+        ws, dtype = self.rt.workspace, self.rt.dtype
+        if isinstance(normed, torch.Tensor):
+            h = normed
+        else:
+            h = ws.take(x.shape, dtype)
+            if normed is not None:
+                ops.finish_norm(normed, h)
+            else:
+                self.norm1.forward(x, h)
+        side = self.side is not None
+        y = ws.take(x.shape, torch.float32)
+        self.mixer.forward(h, y, batch, cache, accumulate=False)
+        last = self.ffn is None
+        # after the last sublayer: the token's second input reads x itself; without one, the next block's norm
+        after = (None if side else next_norm) if last else self.norm2.shareable()
+        h = self._join(y, h, self.gate1, self.gate1_b, self.post1, x, after, want_h=not last or side or next_norm is not None)
+        if not last:
+            y = ws.take(x.shape, torch.float32)
+            self.ffn.forward(h, y, batch, accumulate=False)
+            h = self._join(y, h, self.gate2, self.gate2_b, self.post2, x, None if side else next_norm,
+                           want_h=side or next_norm is not None)
+        if side:
+            if self.side_table is None:
+                raise ConfigError("the block's second token input needs the model's table")
+            m = self.side.dim
+            s = ws.take((x.shape[0], m), torch.float32)
+            ops.gemm(h, self.side_gate, s, ops.EPI_STORE_F32, scratch=ws.take)
+            g = ws.take((x.shape[0], m), dtype)
+            ops.token_gate(s, self.side_table, self.side.column0, batch.token_ids, g)
+            y = ws.take(x.shape, torch.float32)
+            ops.gemm(g, self.side_proj, y, ops.EPI_STORE_F32, scratch=ws.take)
+            h = ws.take(x.shape, dtype) if next_norm is not None else None
+            ops.gated_norm_residual(y, self.side_norm, self.side.eps, x, dtype, next_norm=next_norm, h=h)
+        return h if next_norm is not None else None
+
+
+register_part("block", "sandwich", SandwichBlock)
 register_part("block", "parallel", ParallelBlock)
 register_part("block", "prenorm", PreNormBlock)
 register_part("block", "sublayer_norm", SublayerNormBlock)

@@ -10,7 +10,8 @@ Options of the spec: sigmoid scores; groups of experts of which only the best st
 a factor on the weights; gated experts, out_e = Down_e (act(Gate_e h) * (Up_e h)), whose gate and up
 rows are stored in one [E, 2F, D] stack, in turn in groups of 8 (the dense gated feed-forward's layout,
 which the tensor-core products' epilogues read) or, where F is no multiple of 8, all gate rows first; a
-shared dense feed-forward that every token passes and that is added to the experts' sum.
+shared dense feed-forward that every token passes and that is added to the experts' sum; a clamped gated
+activation with a limit L, min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1).
 """
 
 from __future__ import annotations
@@ -34,6 +35,9 @@ class RoutedFeedForward(FeedForward):
         if spec.activation not in ops.ACTIVATIONS:
             raise ConfigError(f"unknown activation {spec.activation!r}: {', '.join(ops.ACTIVATIONS)}")
         self.act = ops.ACTIVATIONS[spec.activation]
+        self.act_limit = float(getattr(spec, "act_limit", 0.0))
+        if self.act == ops.ACT_SWISH_CLAMP and not (spec.gated and self.act_limit > 0.0):
+            raise ConfigError("the clamped activation is a gated expert's and needs its limit (> 0)")
         if spec.score not in SCORES:
             raise ConfigError(f"unknown router score {spec.score!r}: {', '.join(SCORES)}")
         if len(spec.expert_names) != (3 if spec.gated else 2):
@@ -92,10 +96,12 @@ class RoutedFeedForward(FeedForward):
         if ops.moe_tc_ok(h, self.up, s.top_k, self.gated, self.act):
             ops.moe_experts_tc(h, self.up, self.down, ids, weights, residual, accumulate, ws.take)
         elif ops.moe_grouped_ok(h, self.up, self.gated):
-            ops.moe_experts_grouped(h, self.up, self.down, ids, weights, residual, self.act, accumulate, ws.take, gated=self.gated)
+            ops.moe_experts_grouped(h, self.up, self.down, ids, weights, residual, self.act, accumulate, ws.take, gated=self.gated,
+                                    act_limit=self.act_limit)
         else:
             mid = ws.take((T * s.top_k, s.expert_size), h.dtype)
-            ops.moe_experts(h, self.up, self.down, ids, weights, mid, residual, self.act, accumulate, gated=self.gated)
+            ops.moe_experts(h, self.up, self.down, ids, weights, mid, residual, self.act, accumulate, gated=self.gated,
+                            act_limit=self.act_limit)
         if self.shared is not None:
             self.shared.forward(h, residual, batch, accumulate=True)
 

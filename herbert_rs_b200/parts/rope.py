@@ -74,10 +74,23 @@ register_part("position", "rope", RotaryEncoding)
 register_part("position", "scaled_rope", ScaledRotary)
 
 
-def pair_frequencies(rotary_dim: int, theta: float, linear_factor: float = 1.0) -> torch.Tensor:
-    """theta^(-2m / rotary_dim) / linear_factor for m < rotary_dim / 2, computed in float64, as float32."""
+def pair_frequencies(rotary_dim: int, theta: float, linear_factor: float = 1.0, band_scaling=None) -> torch.Tensor:
+    """theta^(-2m / rotary_dim) / linear_factor for m < rotary_dim / 2, computed in float64, as float32.
+    `band_scaling` (factor, low, high, original): a frequency whose wavelength l = 2 pi / f is shorter than
+    original / high stays, one longer than original / low is divided by factor, and between the two it is
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
     m = torch.arange(rotary_dim // 2, dtype=torch.float64)
     f = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * m / rotary_dim) / float(linear_factor)
+    if band_scaling is not None:
+        import math
+        factor, low, high, original = (float(v) for v in band_scaling)
+        if not (factor > 0.0 and original > 0.0 and high > low >= 0.0):
+            raise ConfigError(f"band scaling of rotary frequencies needs factor > 0, original > 0 and high > low >= 0, got {band_scaling}")
+        wavelength = 2.0 * math.pi / f
+        s = (original / wavelength - low) / (high - low)
+        mixed = (1.0 - s) * f / factor + s * f
+        long_ = wavelength > original / low if low > 0.0 else torch.zeros_like(f, dtype=torch.bool)
+        f = torch.where(wavelength < original / high, f, torch.where(long_, f / factor, mixed))
     return f.to(torch.float32)
 
 
@@ -92,7 +105,8 @@ class RotaryPairs(Part):
             raise ConfigError(f"unknown layout of rotated pairs {spec.layout!r}: interleaved, halves")
         self.rotary_dim = spec.rotary_dim
         self.halves = spec.layout == "halves"
-        self.freq = pair_frequencies(spec.rotary_dim, spec.theta, spec.linear_factor).to(rt.device) if spec.rotary_dim else None
+        self.freq = pair_frequencies(spec.rotary_dim, spec.theta, spec.linear_factor,
+                                     getattr(spec, "band_scaling", None)).to(rt.device) if spec.rotary_dim else None
 
 
 register_part("position", "rope_pairs", RotaryPairs)

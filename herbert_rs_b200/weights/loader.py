@@ -106,6 +106,8 @@ def fill_model(model, get, rt: Runtime, round_weights_to_bf16: bool = False) -> 
         model.load_position_table(conv(s.position_table_name))
     if s.pair_embedding is not None:
         model.load_pair_table(conv(s.pair_embedding.table_name))
+    if s.token_side_table is not None:
+        model.load_token_side_table(conv(s.token_side_table[0]))
     for i, block in enumerate(model.blocks):
         prefix = model.block_prefix(i)
         model_names = [n for n in specs if n.startswith(prefix)]
