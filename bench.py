@@ -232,6 +232,31 @@ def _begupel_config(width, heads, kv_heads, dim, vdim, window, scan_heads, scan_
             "embedding": {"bigram": {"buckets": buckets, "mul_prev": 1000003, "mul_cur": 31}}, "layers": layers}
 
 
+def _nefivik_config(width, heads, kv_heads, dim, vdim, window, delta_heads, delta_dim, experts, top, groups, keep, expert_ff,
+                    side, vocab, taps=4):
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "mask": {"size": window}, "conv": taps,
+           "rot": {"base": 10000.0, "dims": dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    delta = {"heads": delta_heads, "dim": delta_dim}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0},
+           "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}}}
+    layers = [{"type": "attention", "mixer": att, "mlp": moe}, {"type": "general_delta", "mixer": delta, "mlp": moe},
+              {"type": "attention", "mixer": dict(att, kv_from=0), "mlp": moe}, {"type": "general_delta", "mixer": delta, "mlp": moe}]
+    return {"architecture": "Nefivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "token_side": {"dim": side},
+            "layers": layers}
+
+
+NEFIVIK_SIZES = {
+    # Nefivik layer sizes (two layers of windowed sigmoid attention, the second reading the first one's keys and values, two of
+    # the generalised delta rule, routed experts in every layer); beside them Begupel (the closest design in its mixers:
+    # windowed attention behind a convolution beside a delta rule, a norm on every sublayer's result), Votapel (the closest
+    # in its feed-forward: gated experts chosen within groups) and the dense decoder, each of the same width, depth, heads
+    # and head size
+    "1k": (dict(width=1024, heads=8, kv_heads=4, dim=128, vdim=128, window=4096, delta_heads=8, delta_dim=128, experts=16, top=2,
+                groups=4, keep=2, expert_ff=768, side=64, vocab=32000), "1k"),
+    "2k": (dict(width=2048, heads=16, kv_heads=8, dim=128, vdim=128, window=4096, delta_heads=16, delta_dim=128, experts=32, top=4,
+                groups=8, keep=4, expert_ff=1408, side=128, vocab=32000), "2k"),
+}
+
 BEGUPEL_SIZES = {
     # Begupel layer sizes (two lightning layers, two with windowed attention beside a gated delta rule); beside them
     # Kebisun with recurrent heads of the same number and sizes (the closest design: a scan over a matrix state, a
@@ -333,6 +358,32 @@ def _launcher_work(name, n, ctx):
             return n * 6.0 * T * (H + 2 * KV) * hd, n * T * ((H + 2 * KV) * hd * (4 + es))
         if name == "hb_gated_rmsnorm":
             return n * 8.0 * T * sh * dv, n * T * sh * dv * (4 + 4 + es)
+    elif ctx["kind"] == "nefivik":
+        H, KV, D = ctx["heads"], ctx["kv_heads"], ctx["width"]
+        hd = max(ctx["dim"], ctx["vdim"])
+        dh, dn = ctx["delta_heads"], ctx["delta_dim"]
+        if name in ("hb_attention_prefill_tc_bf16", "hb_attention_prefill_bf16", "hb_attention_decode_bf16", "hb_attention_simt"):
+            return n * 4.0 * pairs * H * hd, n * (2 * B * L * KV * hd * es + 2 * T * H * hd * es)
+        if name == "hb_general_delta_scan":
+            # 9 operations a state entry and token; a launch reads five key-side vectors and v, writes o, as floats,
+            # and reads and writes every sequence's state
+            return n * 9.0 * T * dh * dn * dn, n * (T * dh * dn * 7 * 4 + 2 * B * dh * dn * dn * 4)
+        if name == "hb_general_delta_prepare":
+            return n * 2.0 * T * dh * dn * 64, n * T * dh * dn * (3 + 5) * 4
+        if name == "hb_gated_norm_residual":
+            return n * 8.0 * T * D, n * T * D * (4 + 4 + 4 + 4 + es)
+        if name == "hb_short_conv":       # q, k, v rows of the storing layer, q rows of the reading one
+            C = (H + KV) * ctx["dim"] + KV * ctx["vdim"]
+            return n * 8.0 * T * C, n / 2.0 * T * (C + H * ctx["dim"]) * 8
+        if name == "hb_qkv_rotary_cache":
+            return n * 6.0 * T * (H + 2 * KV) * hd, n / 2.0 * T * ((2 * H + 2 * KV) * hd * (4 + es))
+        if name == "hb_gated_rmsnorm":
+            return n * 8.0 * T * dh * dn, n * T * dh * dn * (4 + 4 + es)
+        if name in ("hb_moe_experts", "hb_moe_experts_grouped_bf16", "hb_moe_experts_tc_bf16"):
+            E, top, F = ctx["experts"], ctx["top"], ctx["expert_ff"]
+            return n * 6.0 * T * top * F * D, n * (min(E, T * top) * 3 * F * D * es + T * D * (es + 4))
+        if name == "hb_moe_route":
+            return n * 2.0 * T * ctx["experts"] * D, n * (T * D * es + ctx["experts"] * D * es)
     else:
         H, KV, hd, D = ctx["heads"], ctx["kv_heads"], ctx["head_dim"], ctx["width"]
         if name in ("hb_attention_prefill_tc_bf16", "hb_attention_prefill_bf16", "hb_attention_decode_bf16",
@@ -410,9 +461,10 @@ def _design_point(hb, ops, torch, np, cfg, ctx, pk, prompt_len, batch, steps, wa
 
 
 def run_design(args) -> int:
-    """`--design begupel|kebisun|votapel`: prefill and decode of that design at layer sizes that resemble a
+    """`--design begupel|kebisun|nefivik|votapel`: prefill and decode of that design at layer sizes that resemble a
     real model's, beside the dense decoder of equal width, depth and feed-forward width (random weights,
-    bfloat16, four layers each); Begupel also beside Kebisun with recurrent heads of equal sizes."""
+    bfloat16, four layers each); Begupel also beside Kebisun with recurrent heads of equal sizes, Nefivik also beside
+    Begupel and Votapel."""
     import numpy as np
     import torch
 
@@ -424,11 +476,15 @@ def run_design(args) -> int:
     sampler.start()
     result = {}
     table, make = {"kebisun": (DESIGN_SIZES, _kebisun_config), "votapel": (VOTAPEL_SIZES, _votapel_config),
-                   "begupel": (BEGUPEL_SIZES, _begupel_config)}[args.design]
+                   "begupel": (BEGUPEL_SIZES, _begupel_config), "nefivik": (NEFIVIK_SIZES, _nefivik_config)}[args.design]
     for size in (sorted(table) if args.design_size == "all" else [args.design_size]):
         closest = None
+        beside = None
         if args.design == "begupel":
             kb, closest, dense = table[size]
+        elif args.design == "nefivik":
+            kb, beside = table[size]
+            dense = BEGUPEL_SIZES[beside][2]
         else:
             kb, dense = table[size]
         kcfg = make(**kb)
@@ -444,6 +500,11 @@ def run_design(args) -> int:
         if closest is not None:
             result[size]["kebisun"] = _design_point(hb, ops, torch, np, _kebisun_config(**closest), dict(closest, kind="kebisun"), pk,
                                                     args.prompt_len, args.batch, args.steps, args.warmup, windows)
+        if beside is not None:
+            for other, sizes, maker in (("begupel", BEGUPEL_SIZES, _begupel_config), ("votapel", VOTAPEL_SIZES, _votapel_config)):
+                ob = sizes[beside][0]
+                result[size][other] = _design_point(hb, ops, torch, np, maker(**ob), dict(ob, kind=other), pk, args.prompt_len,
+                                                    args.batch, args.steps, args.warmup, windows)
     sampler.stop()
     print(json.dumps({"metric": f"{args.design.capitalize()} and the dense decoder at equal sizes: prefill and decode tokens/s", "unit": "tokens/s",
                       "n_gpus": 1, "impl": "ours", "dtype": "bf16", "data": "synthetic", "steps": args.steps, "warmup": args.warmup,
@@ -473,7 +534,7 @@ def main() -> int:
     ap.add_argument("--pdl-graph", type=int, default=None, help="programmatic dependent launch inside recorded decode steps (0, 1, 2)")
     ap.add_argument("--workload", default=None, choices=["0.6b", "32b"],
                     help="run only this workload of the baseline and print its line")
-    ap.add_argument("--design", default=None, choices=["begupel", "kebisun", "votapel"],
+    ap.add_argument("--design", default=None, choices=["begupel", "kebisun", "nefivik", "votapel"],
                     help="measure this design beside the dense decoder at equal sizes instead of the headline workload")
     ap.add_argument("--design-size", default="all", choices=["all"] + sorted(DESIGN_SIZES))
     args = ap.parse_args()

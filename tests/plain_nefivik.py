@@ -264,10 +264,13 @@ def token_side(x, tokens, layer, W, p, m, eps, dtype, store):
 
 # ---- the model ----------------------------------------------------------------------------------
 class PlainNefivik:
-    def __init__(self, folder: str):
-        with open(os.path.join(folder, "config.json")) as f:
-            self.cfg = json.load(f)
-        self.W = read_safetensors(os.path.join(folder, "model.safetensors"))
+    def __init__(self, folder: str = None, config: dict = None, tensors: dict = None):
+        if folder is not None:
+            with open(os.path.join(folder, "config.json")) as f:
+                config = json.load(f)
+            tensors = read_safetensors(os.path.join(folder, "model.safetensors"))
+        self.cfg = config
+        self.W = {k: v.float() if v.is_floating_point() else v for k, v in tensors.items()}
 
     def layer(self, i, x, tokens, positions, dtype, store, kvs, drop=()):
         c, W = self.cfg, self.W
@@ -308,6 +311,9 @@ class PlainNefivik:
             x = self.layer(i, x, tokens, positions, dtype, store, kvs, drop)
             per_layer.append(x)
         return torch.stack(per_layer), x
+
+    def layers(self, tokens: Sequence[int], dtype=torch.float64):
+        return list(self.hidden(tokens, dtype)[0])
 
     def logits(self, tokens: Sequence[int], dtype=torch.float64, store=None, drop=()):
         store = store or _keep
