@@ -49,7 +49,7 @@ int hb_attention_prefill_bf16(const void* q, int ldq, void* out, int ldo, const 
 int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens, void* out, int ldo, const void* kcache,
     const void* vcache, int n_pages, const int* seq_start, const int* seq_pos0, const int* seq_pages, int
     pages_stride, int n_seqs, int max_q_len, int nh, int nkv, int hd, int page_size, float scale, int window, float
-    softcap, const float* sink, int* error_flag, int* work_counter, void* stream);
+    softcap, const float* sink, const float* gate_bias, int* error_flag, int* work_counter, void* stream);
 
 // attention_simt.cu: attention of any shape on the CUDA cores (the 32-bit path)
 int hb_attention_simt(int dtype, const void* q, int ldq, void* out, int ldo, const void* kcache, const void*
@@ -111,7 +111,8 @@ int hb_gemm_tcgen05_set_workspace(float* floats, int* counters, int ctas);
 int hb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int
     K, int epi, int* error_flag, void* stream);
 int hb_gemm_tcgen05_grouped_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M_max, int
-    N, int K, int E, int epi, const int* rows_used, const int* tile_expert, int* error_flag, void* stream);
+    N, int K, int E, int epi, float glu_limit, const int* rows_used, const int* tile_expert, int* error_flag, void*
+    stream);
 int hb_gemm_tcgen05_qkv_ok(int M, int N);
 int hb_gemm_tcgen05_qkv_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N,
     int K, const float* in_sumsq, int in_parts, int in_stride, float in_eps, const float* qw, const float* kw,
@@ -168,7 +169,7 @@ long long hb_moe_grouped_scratch_ints(int n_tokens, int E, int top);
 int hb_moe_experts_tc_rows(int n_tokens, int E, int top);
 int hb_moe_experts_tc_bf16(const void* h, int ld, const void* up, const void* down, const int* ids, const float*
     weights, int* ints, void* sorted, void* mid, float* part, float* y, int ldy, int n_tokens, int D, int E, int F,
-    int top, int accumulate, int* error_flag, void* stream);
+    int top, float act_limit, int accumulate, int* error_flag, void* stream);
 int hb_moe_experts_grouped_bf16(const void* h, int ld, const void* up, const void* down, const int* ids, const
     float* weights, int* scratch, void* mid, float* part, float* y, int ldy, int n_tokens, int D, int E, int F, int
     top, int act, int gated, float act_limit, int accumulate, void* stream);

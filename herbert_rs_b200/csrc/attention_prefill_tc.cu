@@ -23,7 +23,9 @@
 //              touched between products.
 // Options: a cap on the scores (s <- cap * tanh(s * scale / cap), applied by the row thread before the mask; such
 // scores are then final, times log2 e, and the exponential's multiply-add takes a factor 1), and a sink per
-// query head (the row starts at m = sink, l = 1: a first key without a value).
+// query head (the row starts at m = sink, l = 1: a first key without a value).  With `gate_bias` (a number per query
+// head) there is no softmax: P = sigmoid(s * scale + gate_bias[h]) for a visible key, 0 for a masked one, O = sum P V as it
+// is; no maximum, no sum, and O is never rescaled.
 // A head pair whose second head does not exist (an odd number of query heads per key/value head)
 // runs the first head alone.  CTAs are persistent and take items from a counter, longest first.
 // Every wait on an mbarrier is bounded; a wait that runs out sets *error_flag and the CTA winds down.
@@ -52,6 +54,7 @@ struct PrefillTcArgs {
   int* work_counter;     // next item; zero when the kernel starts, and left at zero by the CTA that fetches last
   float softcap;         // > 0: score <- softcap * tanh(score * scale / softcap)
   const float* sink;     // [nh] or null: e^{sink} joins the row's sum (the row starts at m = sink, l = 1)
+  const float* gate_bias;  // [nh] or null.  Not null: sigmoid weights (see the head of this file)
 };
 
 // One unit of work: 128 consecutive queries of two heads (or one) of one key/value head of one sequence.
@@ -345,6 +348,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // capped scores are brought to their final form (times log2 e) at once; the plain ones keep the
       // scale for the fused multiply-add in front of the exponential
       const float c_log2 = a.softcap > 0.0f ? 1.0f : a.scale_log2;
+      const bool gated = a.gate_bias != nullptr;
+      const float gb_log2 = gated ? a.gate_bias[it.h0 + t] * 1.4426950408889634f : 0.0f;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int ct = c_t + j;
         const int key0 = (tile_lo + j) * PT_KEYS;
@@ -371,13 +376,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           }
         }
         float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains: the instruction's latency is hidden
+        if (!gated) {
 #pragma unroll
-        for (int i = 0; i < PT_KEYS; i += 8)
+          for (int i = 0; i < PT_KEYS; i += 8)
 #pragma unroll
-          for (int q = 0; q < 4; ++q) mxs[q] = max3(mxs[q], s[i + 2 * q], s[i + 2 * q + 1]);
+            for (int q = 0; q < 4; ++q) mxs[q] = max3(mxs[q], s[i + 2 * q], s[i + 2 * q + 1]);
+        }
         float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
         mx *= c_log2;               // the scale is positive: the maximum of the raw scores is the maximum
-        const bool raise = mx > m + PT_RAISE || (m == -INFINITY && mx > -INFINITY);
+        const bool raise = !gated && (mx > m + PT_RAISE || (m == -INFINITY && mx > -INFINITY));
         if (j > 0 && __any_sync(0xffffffffu, raise)) {
           // rescale O to the new maximum (rows that keep theirs: factor 1); the product of the tile before must be complete
           if (!mbar_wait(bar(17 + t), (ct - 1) & 1)) { if (lane == 0) atomicExch(a.error_flag, 29); ok = false; break; }
@@ -401,14 +408,30 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         unsigned pk[PT_KEYS / 2];
         const unsigned long long c2 = pack2(c_log2, c_log2), m2 = pack2(-m_use, -m_use);
         unsigned long long sum2 = pack2(0.0f, 0.0f);
+        if (gated) {
+          // sigmoid(x) = 1 / (1 + 2^(-x log2 e)); a masked score is -inf and weighs exactly 0; the exponent is held below
+          // 2^100 so that the sum stays finite for the fast division
+          const unsigned long long nc2 = pack2(-c_log2, -c_log2), nb2 = pack2(-gb_log2, -gb_log2);
 #pragma unroll
-        for (int i = 0; i < PT_KEYS; i += 2) {
-          float x0, x1;
-          unpack2(fma2(pack2(s[i], s[i + 1]), c2, m2), x0, x1);      // two scores per instruction
-          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
-          sum2 = add2(sum2, pack2(e0, e1));
-          __nv_bfloat162 v = __floats2bfloat162_rn(e0, e1);
-          pk[i >> 1] = *reinterpret_cast<unsigned*>(&v);
+          for (int i = 0; i < PT_KEYS; i += 2) {
+            float x0, x1;
+            unpack2(fma2(pack2(s[i], s[i + 1]), nc2, nb2), x0, x1);
+            const float e0 = fast_exp2(fminf(x0, 100.0f)), e1 = fast_exp2(fminf(x1, 100.0f));
+            const float p0 = (s[i] == -INFINITY) ? 0.0f : __fdividef(1.0f, 1.0f + e0);
+            const float p1 = (s[i + 1] == -INFINITY) ? 0.0f : __fdividef(1.0f, 1.0f + e1);
+            __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+            pk[i >> 1] = *reinterpret_cast<unsigned*>(&v);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < PT_KEYS; i += 2) {
+            float x0, x1;
+            unpack2(fma2(pack2(s[i], s[i + 1]), c2, m2), x0, x1);      // two scores per instruction
+            const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+            sum2 = add2(sum2, pack2(e0, e1));
+            __nv_bfloat162 v = __floats2bfloat162_rn(e0, e1);
+            pk[i >> 1] = *reinterpret_cast<unsigned*>(&v);
+          }
         }
         float sum_a, sum_b;
         unpack2(sum2, sum_a, sum_b);
@@ -428,7 +451,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int ct = c_t + n_tiles - 1;
         if (!mbar_wait(bar(17 + t), ct & 1)) { if (lane == 0) atomicExch(a.error_flag, 36); ok = false; break; }
         tc_fence_after();
-        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        const float inv = gated ? 1.0f : (l > 0.0f ? 1.0f / l : 0.0f);
         bf16* dst = a.out + (size_t)(it.row0 + qi) * a.ldo + (size_t)(it.h0 + t) * HD;
 #pragma unroll
         for (int cc = 0; cc < HD / 32; ++cc) {
@@ -471,7 +494,8 @@ extern "C" int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens
                                             const void* vcache, int n_pages, const int* seq_start, const int* seq_pos0,
                                             const int* seq_pages, int pages_stride, int n_seqs, int max_q_len, int nh,
                                             int nkv, int hd, int page_size, float scale, int window, float softcap,
-                                            const float* sink, int* error_flag, int* work_counter, void* stream) {
+                                            const float* sink, const float* gate_bias, int* error_flag, int* work_counter,
+                                            void* stream) {
   HB_REQUIRE(n_seqs > 0 && max_q_len > 0 && nh > 0 && nkv > 0 && n_tokens > 0 && n_pages > 0, "attention_prefill_tc: sizes must be positive");
   HB_REQUIRE(hd == 64 || hd == 128, "attention_prefill_tc: head size %d is not 64 or 128", hd);
   HB_REQUIRE(nh % nkv == 0, "attention_prefill_tc: %d query heads are not a multiple of %d key/value heads", nh, nkv);
@@ -483,6 +507,7 @@ extern "C" int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens
              "attention_prefill_tc: bad arguments (an error flag and a work counter, one int each, are required)");
   HB_REQUIRE(scale > 0.0f, "attention_prefill_tc: the score scale must be positive");
   HB_REQUIRE(softcap >= 0.0f, "attention_prefill_tc: the cap on the scores must be >= 0 (0: none)");
+  HB_REQUIRE(gate_bias == nullptr || (sink == nullptr && softcap == 0.0f), "attention_prefill_tc: sigmoid weights have no sink and no cap");
   CUtensorMap mq, mk, mv;
   int rc = make_map_cols(&mq, q, n_tokens, nh * hd, ldq, PT_Q);
   if (rc) return rc;
@@ -493,7 +518,7 @@ extern "C" int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens
   if (rc) return rc;
   const int q_tiles = ceil_div(max_q_len, PT_Q);
   PrefillTcArgs a{(bf16*)out, ldo, seq_start, seq_pos0, seq_pages, pages_stride, nh, nkv, page_size,
-                  scale * 1.4426950408889634f, window, error_flag, n_seqs, q_tiles, work_counter, softcap, sink};
+                  scale * 1.4426950408889634f, window, error_flag, n_seqs, q_tiles, work_counter, softcap, sink, gate_bias};
   cudaStream_t s = (cudaStream_t)stream;
   const int pairs = (nh / nkv + 1) / 2;
   const long long items = (long long)q_tiles * n_seqs * nkv * pairs;

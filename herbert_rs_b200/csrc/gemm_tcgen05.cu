@@ -791,10 +791,11 @@ extern "C" int hb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int l
 // A product grouped by expert: A [M_max, K] holds rows sorted by expert, each expert's run padded to whole tiles of
 // 128 rows; W [E * N, K] stacks the experts' matrices; tile i of A (128 rows) is multiplied by the matrix of expert
 // tile_expert[i]; only the first *rows_used rows are computed (both written on the device before this launch).
-// C [M_max, N] (EPI_STORE, EPI_STORE_F32) or [M_max, N / 2] (EPI_SWIGLU).  Rows of padding are computed and mean nothing.
+// C [M_max, N] (EPI_STORE, EPI_STORE_F32) or [M_max, N / 2] (EPI_SWIGLU; with glu_limit > 0 the clamped form of the gated
+// activation).  Rows of padding are computed and mean nothing.
 extern "C" int hb_gemm_tcgen05_grouped_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M_max,
-                                            int N, int K, int E, int epi, const int* rows_used, const int* tile_expert,
-                                            int* error_flag, void* stream) {
+                                            int N, int K, int E, int epi, float glu_limit, const int* rows_used,
+                                            const int* tile_expert, int* error_flag, void* stream) {
   HB_REQUIRE(M_max > 0 && N > 0 && K > 0 && E > 0, "gemm_tcgen05_grouped: sizes must be positive");
   HB_REQUIRE(M_max % TG_BM == 0, "gemm_tcgen05_grouped: %d rows are not whole tiles of %d", M_max, TG_BM);
   HB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05_grouped: K (%d) and the leading dimensions (%d, %d) must be multiples of 8", K, lda, ldw);
@@ -810,7 +811,8 @@ extern "C" int hb_gemm_tcgen05_grouped_bf16(const void* A, int lda, const void* 
   rc = make_map(&mw, W, E * N, K, ldw, BN);
   if (rc) return rc;
   cudaStream_t s = (cudaStream_t)stream;
-  const TgNorm none{};
+  TgNorm none{};
+  none.glu_limit = epi == HB_EPI_SWIGLU ? glu_limit : 0.0f;
   TgGrouped grp;
   grp.rows_used = rows_used;
   grp.tile_expert = tile_expert;

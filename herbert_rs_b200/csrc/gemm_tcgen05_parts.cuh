@@ -31,6 +31,9 @@ struct TgNorm {
   int out_ld;
   float* out_sumsq;        // [2 * ceil(N / BN)][out_stride]: one row per half tile of columns
   int out_stride;
+  // SwiGLU epilogue only.  > 0: the clamped form with this limit L, min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1),
+  // in place of silu(g) u
+  float glu_limit;
 };
 
 // The q/k/v product whose epilogue also does what follows it in an attention layer with heads of
@@ -57,9 +60,15 @@ __device__ __forceinline__ void tg_epilogue32(unsigned (&r)[32], int m, int n, i
       for (int blk = 0; blk < 2; ++blk)
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float gate = __uint_as_float(r[blk * 16 + j]), up = __uint_as_float(r[blk * 16 + 8 + j]);
+          float gate = __uint_as_float(r[blk * 16 + j]), up = __uint_as_float(r[blk * 16 + 8 + j]);
           // silu(g) * u; fast exponential and division: the result is rounded to bfloat16 next
-          y[blk * 8 + j] = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+          if (nm.glu_limit > 0.0f) {
+            gate = fminf(gate, nm.glu_limit);
+            up = fminf(fmaxf(up, -nm.glu_limit), nm.glu_limit) + 1.0f;
+            y[blk * 8 + j] = __fdividef(gate, 1.0f + __expf(-HB_SWISH_CLAMP_SLOPE * gate)) * up;
+          } else {
+            y[blk * 8 + j] = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+          }
         }
       if (n + 32 <= N && ((((size_t)m * ldc + (n >> 1)) & 7) == 0)) {
 #pragma unroll

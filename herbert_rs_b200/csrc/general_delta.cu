@@ -21,11 +21,11 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------------
-// A CTA takes GP_TOK tokens whose low-rank rows (after tanh) it keeps in shared memory; a warp takes one head of
-// one token at a time: its lanes form w and a for their channels (a lane reads its rows of W2 once per token),
-// the warp sums k^2, and the five vectors leave side by side.
-#define GP_TOK 4
-#define GP_WARPS 8
+// A CTA takes one head of GP_TOK tokens, a thread one key channel of it (a head wider than the block: several): the
+// thread reads its row of W2 once for all of the CTA's tokens, whose low-rank rows (after tanh) lie in shared memory;
+// the sums of k^2 go through the block.  Few tokens (a decode step) still spread over heads x token groups CTAs.
+#define GP_TOK 8
+#define GP_MAX_THREADS 256
 struct GdPrepArgs {
   const float* rows; int ld;       // the projection's float rows
   int r_off, k_off, a_off, low_off;
@@ -38,43 +38,71 @@ struct GdPrepArgs {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(GP_WARPS * 32) general_delta_prepare_kernel(GdPrepArgs a) {
+__global__ void __launch_bounds__(GP_MAX_THREADS) general_delta_prepare_kernel(GdPrepArgs a) {
   extern __shared__ float lows[];   // [GP_TOK][rank]
+  __shared__ float red[GP_TOK][GP_MAX_THREADS / 32];
+  __shared__ float inv[GP_TOK];
   pdl_wait();
   pdl_launch();
-  const int t0 = blockIdx.x * GP_TOK;
+  const int t0 = blockIdx.x * GP_TOK, h = blockIdx.y;
   const int nt = a.n_tokens - t0 < GP_TOK ? a.n_tokens - t0 : GP_TOK;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
   for (int i = threadIdx.x; i < nt * a.rank; i += blockDim.x) {
     const int tt = i / a.rank, j = i - tt * a.rank;
     lows[i] = tanhf(a.rows[(size_t)(t0 + tt) * a.ld + a.low_off + j]);
   }
+  // sum of k^2 per token over the head's channels
+  float ss[GP_TOK];
+#pragma unroll
+  for (int tt = 0; tt < GP_TOK; ++tt) ss[tt] = 0.0f;
+  for (int i = threadIdx.x; i < a.dk; i += blockDim.x) {
+#pragma unroll
+    for (int tt = 0; tt < GP_TOK; ++tt)
+      if (tt < nt) {
+        const float k = a.rows[(size_t)(t0 + tt) * a.ld + a.k_off + (size_t)h * a.dk + i];
+        ss[tt] = fmaf(k, k, ss[tt]);
+      }
+  }
+#pragma unroll
+  for (int tt = 0; tt < GP_TOK; ++tt) {
+    const float v = warp_sum(ss[tt]);
+    if (lane == 0) red[tt][warp] = v;
+  }
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x < GP_TOK) {
+    float v = 0.0f;
+    for (int w = 0; w < nwarp; ++w) v += red[threadIdx.x][w];
+    inv[threadIdx.x] = 1.0f / sqrtf(v + a.unit_eps);
+  }
+  __syncthreads();
   const T* w2 = (const T*)a.w2;
-  for (int unit = warp; unit < nt * a.H; unit += GP_WARPS) {
-    const int tt = unit / a.H, h = unit - tt * a.H;
-    const float* row = a.rows + (size_t)(t0 + tt) * a.ld;
-    const float* kk = row + a.k_off + (size_t)h * a.dk;
-    float ss = 0.0f;
-    for (int i = lane; i < a.dk; i += 32) ss = fmaf(kk[i], kk[i], ss);
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss + a.unit_eps);
-    float* out = a.prep + ((size_t)(t0 + tt) * a.H + h) * 5 * a.dk;
-    const float* lw = lows + tt * a.rank;
-    for (int i = lane; i < a.dk; i += 32) {
-      const int c = h * a.dk + i;
-      const T* wr = w2 + (size_t)c * a.rank;
-      float z = a.w0[c];
-      for (int j = 0; j < a.rank; ++j) z = fmaf(lw[j], to_f32(wr[j]), z);
-      const float w = expf(-a.decay_c / (1.0f + expf(-z)));
-      const float rate = 1.0f / (1.0f + expf(-(row[a.a_off + c] + a.a0[c])));
-      const float k = kk[i], u = k * inv;
-      out[i] = row[a.r_off + c];
-      out[a.dk + i] = k;
-      out[2 * a.dk + i] = w;
-      out[3 * a.dk + i] = u;
-      out[4 * a.dk + i] = rate * u;
+  for (int i = threadIdx.x; i < a.dk; i += blockDim.x) {
+    const int c = h * a.dk + i;
+    const T* wr = w2 + (size_t)c * a.rank;
+    float z[GP_TOK];
+    const float z0 = a.w0[c], a0 = a.a0[c];
+#pragma unroll
+    for (int tt = 0; tt < GP_TOK; ++tt) z[tt] = z0;
+    for (int j = 0; j < a.rank; ++j) {
+      const float w = to_f32(wr[j]);
+#pragma unroll
+      for (int tt = 0; tt < GP_TOK; ++tt)
+        if (tt < nt) z[tt] = fmaf(lows[tt * a.rank + j], w, z[tt]);
     }
+#pragma unroll
+    for (int tt = 0; tt < GP_TOK; ++tt)
+      if (tt < nt) {
+        const float* row = a.rows + (size_t)(t0 + tt) * a.ld;
+        float* out = a.prep + ((size_t)(t0 + tt) * a.H + h) * 5 * a.dk;
+        const float w = expf(-a.decay_c / (1.0f + expf(-z[tt])));
+        const float rate = 1.0f / (1.0f + expf(-(row[a.a_off + c] + a0)));
+        const float k = row[a.k_off + c], u = k * inv[tt];
+        out[i] = row[a.r_off + c];
+        out[a.dk + i] = k;
+        out[2 * a.dk + i] = w;
+        out[3 * a.dk + i] = u;
+        out[4 * a.dk + i] = rate * u;
+      }
   }
 }
 
@@ -83,13 +111,15 @@ extern "C" int hb_general_delta_prepare(int dtype, const float* rows, int ld, in
                                         float* prep, int n_tokens, int heads, int dk, int rank, void* stream) {
   HB_REQUIRE(n_tokens > 0 && heads > 0 && dk > 0 && rank > 0, "general_delta_prepare: sizes must be positive");
   const size_t smem = (size_t)GP_TOK * rank * sizeof(float);
-  HB_REQUIRE(smem <= 48 * 1024, "general_delta_prepare: the decay's inner width %d exceeds what a block keeps in shared memory", rank);
+  HB_REQUIRE(smem <= 40 * 1024, "general_delta_prepare: the decay's inner width %d exceeds what a block keeps in shared memory", rank);
+  HB_REQUIRE(heads <= 65535, "general_delta_prepare: too many heads");
   GdPrepArgs a{rows, ld, r_off, k_off, a_off, low_off, w2, w0, a0, decay_c, unit_eps, prep, n_tokens, heads, dk, rank};
-  dim3 grid(ceil_div(n_tokens, GP_TOK));
+  dim3 grid(ceil_div(n_tokens, GP_TOK), heads);
+  const int threads = dk >= GP_MAX_THREADS ? GP_MAX_THREADS : ceil_div(dk, 32) * 32;
   if (dtype == HB_F32)
-    hb_launch(general_delta_prepare_kernel<float>, grid, dim3(GP_WARPS * 32), smem, (cudaStream_t)stream, a);
+    hb_launch(general_delta_prepare_kernel<float>, grid, dim3(threads), smem, (cudaStream_t)stream, a);
   else
-    hb_launch(general_delta_prepare_kernel<bf16>, grid, dim3(GP_WARPS * 32), smem, (cudaStream_t)stream, a);
+    hb_launch(general_delta_prepare_kernel<bf16>, grid, dim3(threads), smem, (cudaStream_t)stream, a);
   HB_CHECK_LAUNCH("general_delta_prepare");
   return 0;
 }

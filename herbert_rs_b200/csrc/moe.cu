@@ -466,7 +466,8 @@ extern "C" int hb_moe_experts_grouped_bf16(const void* h, int ld, const void* up
 }
 
 // ---------------------------------------------------------------------------------------------
-// Long prompts, gated experts with silu, bfloat16: the grouped products on tcgen05.  The pairs are sorted by
+// Long prompts, gated experts with silu (act_limit 0) or the clamped activation (act_limit L > 0), bfloat16: the grouped
+// products on tcgen05.  The pairs are sorted by
 // expert into a buffer in which every expert's run is padded to whole tiles of 128 rows, so that a tile of the
 // tensor-memory product (gemm_tcgen05.cu, grouped mode) belongs to one expert:
 //   sort:     counts per expert, padded offsets, slot[pair] = its row, tile_expert[tile], rows in use
@@ -524,8 +525,8 @@ extern "C" int hb_moe_experts_tc_rows(int n_tokens, int E, int top) {
 // mid [rows, F] bfloat16, part [rows, D] floats, with rows = hb_moe_experts_tc_rows(...).
 extern "C" int hb_moe_experts_tc_bf16(const void* h, int ld, const void* up, const void* down, const int* ids,
                                       const float* weights, int* ints, void* sorted, void* mid, float* part, float* y, int ldy,
-                                      int n_tokens, int D, int E, int F, int top, int accumulate, int* error_flag,
-                                      void* stream) {
+                                      int n_tokens, int D, int E, int F, int top, float act_limit, int accumulate,
+                                      int* error_flag, void* stream) {
   HB_REQUIRE(n_tokens > 0 && D > 0 && E > 0 && F > 0 && top > 0, "moe_experts_tc: sizes must be positive");
   HB_REQUIRE(E <= MG_MAX_EXPERTS, "moe_experts_tc: at most %d experts", MG_MAX_EXPERTS);
   HB_REQUIRE(D % 8 == 0 && F % 8 == 0 && ld % 8 == 0 && ((uintptr_t)h & 15) == 0, "moe_experts_tc: widths must be multiples of 8, rows 16-byte aligned");
@@ -541,10 +542,10 @@ extern "C" int hb_moe_experts_tc_bf16(const void* h, int ld, const void* up, con
   hb_launch(moe_gather_rows_kernel, dim3(n_pairs), dim3(D / 8 >= 128 ? 128 : 64), 0, s, (const bf16*)h, ld, (const int*)slot,
             (bf16*)sorted, D / 8, top);
   HB_CHECK_LAUNCH("moe_experts_tc (sort, gather)");
-  int rc = hb_gemm_tcgen05_grouped_bf16(sorted, D, up, D, mid, F, rows, 2 * F, D, E, HB_EPI_SWIGLU, rows_used, tile_expert,
-                                        error_flag, stream);
+  int rc = hb_gemm_tcgen05_grouped_bf16(sorted, D, up, D, mid, F, rows, 2 * F, D, E, HB_EPI_SWIGLU, act_limit, rows_used,
+                                        tile_expert, error_flag, stream);
   if (rc) return rc;
-  rc = hb_gemm_tcgen05_grouped_bf16(mid, F, down, F, part, D, rows, D, F, E, HB_EPI_STORE_F32, rows_used, tile_expert,
+  rc = hb_gemm_tcgen05_grouped_bf16(mid, F, down, F, part, D, rows, D, F, E, HB_EPI_STORE_F32, 0.0f, rows_used, tile_expert,
                                     error_flag, stream);
   if (rc) return rc;
   hb_launch(moe_combine_kernel, dim3(ceil_div(D, 256), n_tokens), dim3(256), 0, s, (const float*)part, weights, y, ldy, D, top,

@@ -67,7 +67,7 @@ _SIGS = {
                                   c_void_p],
     "hb_attention_prefill_tc_bf16": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p,
-                                     c_void_p, c_void_p, c_void_p],
+                                     c_void_p, c_void_p, c_void_p, c_void_p],
     "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p],
     "hb_gemm_skinny_norm_parts": [c_int, c_int],
     "hb_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -88,7 +88,7 @@ _SIGS = {
                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_moe_experts_tc_rows": [c_int, c_int, c_int],
     "hb_moe_experts_tc_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "hb_latent_attention_mma_ok": [c_int, c_int],
     "hb_latent_attention_mma_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
@@ -745,15 +745,16 @@ def moe_grouped_ok(h, up, gated=0) -> bool:
 
 
 def moe_tc_ok(h, up, top, gated, act) -> bool:
-    """Whether the grouped products run on tcgen05: what `moe_grouped_ok` asks, gated experts with silu (the
-    product's fused epilogue), and enough (token, expert) pairs that tiles of 128 rows per expert fill."""
-    return (options.moe_tc and moe_grouped_ok(h, up, gated) and gated == GATED_GROUPS_OF_8 and act == ACT_SILU
+    """Whether the grouped products run on tcgen05: what `moe_grouped_ok` asks, gated experts with silu or the clamped
+    activation (the product's fused epilogue), and enough (token, expert) pairs that tiles of 128 rows per expert fill."""
+    return (options.moe_tc and moe_grouped_ok(h, up, gated) and gated == GATED_GROUPS_OF_8 and act in (ACT_SILU, ACT_SWISH_CLAMP)
             and h.shape[0] * int(top) >= MOE_TC_MIN_PAIRS)
 
 
-def moe_experts_tc(h, up, down, ids, weights, y, accumulate, scratch) -> None:
-    """moe_experts for long prompts, gated experts with silu: the pairs sorted by expert into runs padded to tiles of
-    128 rows, both products on tcgen05 (the first with the gated activation in its epilogue)."""
+def moe_experts_tc(h, up, down, ids, weights, y, accumulate, scratch, act_limit=0.0) -> None:
+    """moe_experts for long prompts, gated experts with silu (or, with act_limit > 0, the clamped activation): the pairs
+    sorted by expert into runs padded to tiles of 128 rows, both products on tcgen05 (the first with the gated
+    activation in its epilogue)."""
     _check(h, torch.bfloat16, "h"); _check(up, torch.bfloat16, "up"); _check(down, torch.bfloat16, "down"); _check(y, torch.float32, "y")
     T, top = ids.shape
     E, F2, D = up.shape
@@ -768,7 +769,7 @@ def moe_experts_tc(h, up, down, ids, weights, y, accumulate, scratch) -> None:
     _tcgen05_workspace(y.device)
     _run("hb_moe_experts_tc_bf16", h.data_ptr(), h.stride(0), up.data_ptr(), down.data_ptr(), ids.data_ptr(), weights.data_ptr(),
          ints.data_ptr(), srt.data_ptr(), mid.data_ptr(), part.data_ptr(), y.data_ptr(), y.stride(0), T, D, E, F, top,
-         1 if accumulate else 0, _error_flag(y.device).data_ptr(), _stream())
+         float(act_limit), 1 if accumulate else 0, _error_flag(y.device).data_ptr(), _stream())
 
 
 def moe_experts_grouped(h, up, down, ids, weights, y, act, accumulate, scratch, gated=0, act_limit=0.0) -> None:
@@ -1271,16 +1272,19 @@ def attention_prefill(q, ldq, out, k_cache, v_cache, seq_start, seq_pos0, seq_pa
 
 
 def attention_prefill_tc(q, ldq, out, k_cache, v_cache, seq_start, seq_pos0, seq_pages, n_seqs, max_q_len,
-                         num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap=None, sink=None) -> None:
+                         num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap=None, sink=None,
+                         gate_bias=None) -> None:
     """The same on tcgen05 tensor cores (head sizes 64 and 128): S and O in tensor memory."""
     _check(out, torch.bfloat16, "out")
     if sink is not None:
         _check(sink, torch.float32, "sink")
+    if gate_bias is not None:
+        _check(gate_bias, torch.float32, "gate_bias")
     _run("hb_attention_prefill_tc_bf16", q.data_ptr(), int(ldq), q.shape[0], out.data_ptr(), out.stride(0),
          k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[0], seq_start.data_ptr(), seq_pos0.data_ptr(),
          seq_pages.data_ptr(), seq_pages.stride(0), int(n_seqs), int(max_q_len), num_heads, num_kv_heads, head_dim,
-         page_size, float(scale), int(window or 0), float(softcap or 0.0), _ptr(sink), _error_flag(out.device).data_ptr(),
-         _work_counter(out.device).data_ptr(), _stream())
+         page_size, float(scale), int(window or 0), float(softcap or 0.0), _ptr(sink), _ptr(gate_bias),
+         _error_flag(out.device).data_ptr(), _work_counter(out.device).data_ptr(), _stream())
 
 
 _work_counters: dict = {}
@@ -1329,9 +1333,9 @@ def attention(q, ldq, out, k_cache, v_cache, batch, num_heads, num_kv_heads, hea
         attention_decode(q, ldq, out, k_cache, v_cache, batch.seq_len, seq_pages, buf, num_heads, num_kv_heads,
                          head_dim, page_size, nsplit, scale, window, softcap, sink, gate_bias)
         return
-    if gate_bias is None and _prefill_tc_ok(q, ldq, out, head_dim, page_size):
+    if _prefill_tc_ok(q, ldq, out, head_dim, page_size):
         attention_prefill_tc(q, ldq, out, k_cache, v_cache, batch.seq_start, batch.seq_pos0, seq_pages, batch.n_seqs,
-                             batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap, sink)
+                             batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap, sink, gate_bias)
         return
     if _prefill_kernel_ok(out, head_dim, page_size):
         attention_prefill(q, ldq, out, k_cache, v_cache, batch.seq_start, batch.seq_pos0, seq_pages, batch.n_seqs,

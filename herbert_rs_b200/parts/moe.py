@@ -94,7 +94,8 @@ class RoutedFeedForward(FeedForward):
         ops.moe_route(h, self.router, ids, weights, s.top_k, s.renormalize, SCORES[s.score], s.groups, s.keep_groups,
                       s.group_top, s.weight_scale)
         if ops.moe_tc_ok(h, self.up, s.top_k, self.gated, self.act):
-            ops.moe_experts_tc(h, self.up, self.down, ids, weights, residual, accumulate, ws.take)
+            ops.moe_experts_tc(h, self.up, self.down, ids, weights, residual, accumulate, ws.take,
+                               act_limit=self.act_limit if self.act == ops.ACT_SWISH_CLAMP else 0.0)
         elif ops.moe_grouped_ok(h, self.up, self.gated):
             ops.moe_experts_grouped(h, self.up, self.down, ids, weights, residual, self.act, accumulate, ws.take, gated=self.gated,
                                     act_limit=self.act_limit)

@@ -248,9 +248,10 @@ def test_sigmoid_weights_in_every_attention_kernel(H, G, dk, dv, window):
         qq = torch.zeros(T, H, hd)
         qq[:, :, :dk] = q
         qd = qq.view(T, H * hd).to(td_of(dtype)).to(DEV)
-        kernels = ["simt"] + (["auto"] if dtype == "bfloat16" else [])
+        kernels = ["simt"] + (["auto", "mma"] if dtype == "bfloat16" else [])      # "auto": tcgen05 for prompts of heads of 64 / 128
         for kern in kernels:
-            ops.options.attention = kern
+            ops.options.attention = "simt" if kern == "simt" else "auto"
+            ops.options.prefill_attention = "mma" if kern == "mma" else "tcgen05"
             try:
                 batch = step_of([70], [0], [T - 70])
                 out = torch.empty(70, H * hd, dtype=td_of(dtype), device=DEV)
@@ -265,8 +266,9 @@ def test_sigmoid_weights_in_every_attention_kernel(H, G, dk, dv, window):
                               scratch=lambda shape, dt: torch.empty(shape, dtype=dt, device=DEV), gate_bias=bias.to(DEV))
                 got = to_np(out).reshape(1, H, hd)[:, :, :dv]
                 assert np.abs(got - ref[[last]].numpy()).max() < bound, (dtype, kern, "alone")
+                ops.check_kernel_errors()
             finally:
-                ops.options.attention = "auto"
+                ops.options.attention, ops.options.prefill_attention = "auto", "tcgen05"
     if window and 1 < window < T:
         # the window shows: one key more moves the last row far beyond any bound
         a = P.sigmoid_attention(q.double(), k.double().transpose(0, 1), v.double().transpose(0, 1), scale, window + 1, bias.double())
@@ -274,7 +276,7 @@ def test_sigmoid_weights_in_every_attention_kernel(H, G, dk, dv, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,E,top,F,D", [(5, 6, 2, 24, 64), (70, 12, 3, 64, 320), (40, 4, 4, 8, 48)])
+@pytest.mark.parametrize("T,E,top,F,D", [(5, 6, 2, 24, 64), (70, 12, 3, 64, 320), (40, 4, 4, 8, 48), (300, 12, 3, 64, 320)])
 def test_clamped_experts_few_tokens_and_grouped(dtype, T, E, top, F, D):
     g = torch.Generator().manual_seed(T + E)
     limit = 1.25
@@ -307,6 +309,12 @@ def test_clamped_experts_few_tokens_and_grouped(dtype, T, E, top, F, D):
         ops.moe_experts_grouped(hd_, up, down, idd, wd, y2, ops.ACT_SWISH_CLAMP, True, lambda s, dt: torch.empty(s, dtype=dt, device=DEV),
                                 gated=layout, act_limit=limit)
         assert_close(to_np(y2) - 1.0, ref.numpy(), dtype, "grouped experts")
+    if dtype == "bfloat16" and ops.moe_tc_ok(hd_, up, top, layout, ops.ACT_SWISH_CLAMP):
+        y3 = torch.ones(T, D, device=DEV)
+        ops.moe_experts_tc(hd_, up, down, idd, wd, y3, True, lambda s, dt: torch.empty(s, dtype=dt, device=DEV), act_limit=limit)
+        ops.check_kernel_errors()
+        assert_close(to_np(y3) - 1.0, ref.numpy(), dtype, "experts on tcgen05")
+        assert T * top >= 512
 
 
 @pytest.mark.parametrize("E,groups,keep,top", [(12, 3, 2, 3), (6, 3, 2, 2), (8, 1, 1, 8), (8, 8, 3, 3), (4, 2, 1, 2), (5, 1, 1, 1)])
