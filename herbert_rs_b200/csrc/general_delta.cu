@@ -156,6 +156,7 @@ struct GdScanArgs {
 template <int RPT>
 __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(GdScanArgs a) {
   extern __shared__ __align__(16) float sh[];
+  __shared__ float outs[GD_CHUNK * GD_THREADS];                   // [GD_CHUNK][cols]: a chunk's read-outs
   const int R = a.R, DKP = R * RPT, cols = GD_THREADS / R;
   const int stage_floats = GD_CHUNK * (5 * DKP + cols);
   pdl_wait();
@@ -214,6 +215,10 @@ __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(GdScanAr
     __syncthreads();
     const float* ks = sh + buf * stage_floats;
     const float* vs = ks + GD_CHUNK * 5 * DKP;
+    // Only `seen` of one token stands between it and the next: the read-out's sum and its shuffles belong to no chain, so
+    // the loop is unrolled for them to run beside the next token's first sum; the results leave through an array of their
+    // own in shared memory (a store into global memory in the loop would keep the next tokens' loads behind it).
+#pragma unroll 4
     for (int tt = 0; tt < n; ++tt) {
       const float4* r4 = reinterpret_cast<const float4*>(ks + (tt * 5 + 0) * DKP) + rg;
       const float4* k4 = reinterpret_cast<const float4*>(ks + (tt * 5 + 1) * DKP) + rg;
@@ -236,14 +241,19 @@ __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(GdScanAr
 #pragma unroll
       for (int i = 0; i < RPT / 4; ++i) {
         const float4 w = w4[i * R], p = p4[i * R], k = k4[i * R], r = r4[i * R];
-        s[4 * i] = fmaf(k.x, v, fmaf(-p.x, seen, w.x * s[4 * i]));                 o0 = fmaf(s[4 * i], r.x, o0);
-        s[4 * i + 1] = fmaf(k.y, v, fmaf(-p.y, seen, w.y * s[4 * i + 1]));         o1 = fmaf(s[4 * i + 1], r.y, o1);
-        s[4 * i + 2] = fmaf(k.z, v, fmaf(-p.z, seen, w.z * s[4 * i + 2]));         o2 = fmaf(s[4 * i + 2], r.z, o2);
-        s[4 * i + 3] = fmaf(k.w, v, fmaf(-p.w, seen, w.w * s[4 * i + 3]));         o3 = fmaf(s[4 * i + 3], r.w, o3);
+        s[4 * i] = fmaf(w.x, s[4 * i], fmaf(-p.x, seen, k.x * v));                 o0 = fmaf(s[4 * i], r.x, o0);
+        s[4 * i + 1] = fmaf(w.y, s[4 * i + 1], fmaf(-p.y, seen, k.y * v));         o1 = fmaf(s[4 * i + 1], r.y, o1);
+        s[4 * i + 2] = fmaf(w.z, s[4 * i + 2], fmaf(-p.z, seen, k.z * v));         o2 = fmaf(s[4 * i + 2], r.z, o2);
+        s[4 * i + 3] = fmaf(w.w, s[4 * i + 3], fmaf(-p.w, seen, k.w * v));         o3 = fmaf(s[4 * i + 3], r.w, o3);
       }
       float o = (o0 + o1) + (o2 + o3);
       for (int w = R >> 1; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
-      if (rg == 0 && col < a.dv) a.out[(size_t)(c0 + tt) * a.ldo + h * a.dv + col] = o;
+      if (rg == 0) outs[tt * cols + cl] = o;
+    }
+    __syncthreads();
+    for (int i = tid; i < n * cols; i += GD_THREADS) {
+      const int tt = i >> cshift, c = blockIdx.z * cols + (i & (cols - 1));
+      if (c < a.dv) a.out[(size_t)(c0 + tt) * a.ldo + h * a.dv + c] = outs[i];
     }
     __syncthreads();
   }
@@ -272,13 +282,13 @@ extern "C" int hb_general_delta_scan(const float* prep, const float* v, int ldv,
   const int cols = GD_THREADS / R;
   HB_REQUIRE(heads <= 65535 && ceil_div(dv, cols) <= 65535, "general_delta_scan: too many heads or value channels");
   const size_t smem = (size_t)2 * GD_CHUNK * (5 * R * rpt + cols) * sizeof(float);
-  HB_REQUIRE(smem <= 200 * 1024, "general_delta_scan: %d key channels per head need %zu bytes of shared memory, more than a CTA has", dk, smem);
+  HB_REQUIRE(smem <= 192 * 1024, "general_delta_scan: %d key channels per head need %zu bytes of shared memory, more than a CTA has", dk, smem);
   GdScanArgs a{prep, v, ldv, state, seq_slot, seq_start, out, ldo, heads, dk, dv, R};
   dim3 grid(n_seqs, heads, ceil_div(dv, cols));
   cudaStream_t s = (cudaStream_t)stream;
 #define GD_GO(RPT)                                                                                                         \
   do {                                                                                                                     \
-    if (smem > 48 * 1024) cudaFuncSetAttribute(general_delta_scan_kernel<RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (smem > 32 * 1024) cudaFuncSetAttribute(general_delta_scan_kernel<RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     hb_launch(general_delta_scan_kernel<RPT>, grid, dim3(GD_THREADS), smem, s, a);                                         \
   } while (0)
   if (rpt == 4) GD_GO(4); else if (rpt == 8) GD_GO(8); else if (rpt == 16) GD_GO(16); else GD_GO(32);
