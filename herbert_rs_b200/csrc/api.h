@@ -32,8 +32,7 @@ extern "C" {
 long long hb_attention_decode_scratch_floats(int n_seqs, int nh, int hd, int nsplit);
 int hb_attention_decode_bf16(const void* q, int ldq, void* out, int ldo, const void* kcache, const void* vcache,
     const int* seq_len, const int* seq_pages, int pages_stride, float* scratch, int n_seqs, int nh, int nkv, int hd,
-    int page_size, int nsplit, float scale, int window, float softcap, const float* sink, const float* gate_bias, void*
-    stream);
+    int page_size, int nsplit, float scale, int window, float softcap, const float* sink, const float* gate_bias, const float* out_gate, int ldg, void* stream);
 int hb_attention_decode_fused_bf16(const void* qkv, int ld, void* out, int ldo, void* kcache, void* vcache,
     const float* qw, const float* kw, float eps, const float* cos_tab, const float* sin_tab, int table_rows,
     int write_cache, const int* seq_len, const int* seq_pages, int pages_stride, float* scratch, int*
@@ -42,20 +41,18 @@ int hb_attention_decode_fused_bf16(const void* qkv, int ld, void* out, int ldo, 
 // attention_prefill.cu: prefill attention, mma.sync flash form, head sizes in steps of 16 up to 256
 int hb_attention_prefill_bf16(const void* q, int ldq, void* out, int ldo, const void* kcache, const void* vcache,
     const int* seq_start, const int* seq_pos0, const int* seq_pages, int pages_stride, int n_seqs, int max_q_len, int
-    nh, int nkv, int hd, int page_size, float scale, int window, float softcap, const float* sink, const float*
-    gate_bias, void* stream);
+    nh, int nkv, int hd, int page_size, float scale, int window, float softcap, const float* sink, const float* gate_bias, const float* out_gate, int ldg, void* stream);
 
 // attention_prefill_tc.cu: prefill attention on tcgen05 tensor cores, head sizes 64 and 128
 int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens, void* out, int ldo, const void* kcache,
     const void* vcache, int n_pages, const int* seq_start, const int* seq_pos0, const int* seq_pages, int
     pages_stride, int n_seqs, int max_q_len, int nh, int nkv, int hd, int page_size, float scale, int window, float
-    softcap, const float* sink, const float* gate_bias, int* error_flag, int* work_counter, void* stream);
+    softcap, const float* sink, const float* gate_bias, const float* out_gate, int ldg, int* error_flag, int* work_counter, void* stream);
 
 // attention_simt.cu: attention of any shape on the CUDA cores (the 32-bit path)
 int hb_attention_simt(int dtype, const void* q, int ldq, void* out, int ldo, const void* kcache, const void*
     vcache, const int* tok_seq, const int* tok_pos, const int* seq_pages, int pages_stride, int n_tokens, int nh, int
-    nkv, int hd, int page_size, float scale, int window, float softcap, const float* sink, const float* gate_bias,
-    void* stream);
+    nkv, int hd, int page_size, float scale, int window, float softcap, const float* sink, const float* gate_bias, const float* out_gate, int ldg, void* stream);
 
 // elementwise.cu: embedding, RMSNorm, SwiGLU, head norm + rotation + cache write, residual sum, shared-norm finish
 int hb_embed(int dtype, const void* table, const int* ids, float* out, int n_tokens, int hidden, int vocab, float

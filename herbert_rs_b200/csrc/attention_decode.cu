@@ -664,7 +664,8 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
 // denominator here, once, whatever the number of splits: m covers it and e^{sink - m} is added.
 __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                 bf16* __restrict__ out, int ldo, int nh, int hd, int nsplit,
-                                                const float* __restrict__ sink, int gated) {
+                                                const float* __restrict__ sink, int gated, const float* __restrict__ out_gate,
+                                                int ldg) {
   pdl_wait();
   pdl_launch();
   const int h = blockIdx.x, b = blockIdx.y;
@@ -676,7 +677,8 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o
     const float ms = part_ml[(base + s) * 2];
     if (ms != -INFINITY) ll += __expf(ms - mm) * part_ml[(base + s) * 2 + 1];
   }
-  const float inv = gated ? 1.0f : (ll > 0.0f ? 1.0f / ll : 0.0f);    // sigmoid weights: every m is 0, the partial sums add up
+  float inv = gated ? 1.0f : (ll > 0.0f ? 1.0f / ll : 0.0f);    // sigmoid weights: every m is 0, the partial sums add up
+  if (out_gate != nullptr) inv *= 1.0f / (1.0f + expf(-out_gate[(size_t)b * ldg + h]));      // a gate per token and head
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float acc = 0.0f;
     for (int s = 0; s < nsplit; ++s) {
@@ -705,7 +707,8 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
                                         const void* vcache, const int* seq_len, const int* seq_pages,
                                         int pages_stride, float* scratch, int n_seqs, int nh, int nkv, int hd,
                                         int page_size, int nsplit, float scale, int window, float softcap,
-                                        const float* sink, const float* gate_bias, void* stream) {
+                                        const float* sink, const float* gate_bias, const float* out_gate, int ldg,
+                                        void* stream) {
   HB_REQUIRE(n_seqs > 0 && nh > 0 && nkv > 0 && hd > 0, "attention_decode: sizes must be positive");
   HB_REQUIRE(softcap >= 0.0f, "attention_decode: the cap on the scores must be >= 0 (0: none)");
   HB_REQUIRE(gate_bias == nullptr || sink == nullptr, "attention_decode: sigmoid weights have no sink");
@@ -753,7 +756,8 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
   }
   HB_CHECK_LAUNCH("attention_decode");
   dim3 cgrid(nh, n_seqs);
-  hb_launch(attention_decode_combine_kernel, dim3(cgrid), dim3(hd >= 128 ? 128 : 64), 0, s, part_o, part_ml, (bf16*)out, ldo, nh, hd, nsplit, sink, gate_bias != nullptr ? 1 : 0);
+  hb_launch(attention_decode_combine_kernel, dim3(cgrid), dim3(hd >= 128 ? 128 : 64), 0, s, part_o, part_ml, (bf16*)out, ldo, nh, hd, nsplit, sink, gate_bias != nullptr ? 1 : 0,
+            out_gate, ldg);
   HB_CHECK_LAUNCH("attention_decode_combine");
   return 0;
 }

@@ -43,6 +43,8 @@ struct PrefillArgs {
   float softcap;       // > 0: score <- softcap * tanh(score / softcap) after the scale
   const float* sink;   // [nh] or null: e^{sink} joins the row's sum (m starts at the sink, l at 1)
   const float* gate_bias;  // [nh] or null.  Not null: no softmax; a visible key weighs sigmoid(score + gate_bias[h]) as it is
+  const float* out_gate;   // [tokens, ldg] or null: head h's result of a token is multiplied by sigmoid(out_gate[token * ldg + h])
+  int ldg;
 };
 
 template <int HDM>
@@ -254,7 +256,11 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(PrefillAr
   }
   cp_async_wait<0>();
 
-  const float inv0 = gated ? 1.0f : (l[0] > 0.0f ? 1.0f / l[0] : 0.0f), inv1 = gated ? 1.0f : (l[1] > 0.0f ? 1.0f / l[1] : 0.0f);
+  float inv0 = gated ? 1.0f : (l[0] > 0.0f ? 1.0f / l[0] : 0.0f), inv1 = gated ? 1.0f : (l[1] > 0.0f ? 1.0f / l[1] : 0.0f);
+  if (a.out_gate != nullptr) {
+    if (v0) inv0 *= 1.0f / (1.0f + expf(-a.out_gate[(size_t)(row0 + qi0) * a.ldg + h]));
+    if (v1) inv1 *= 1.0f / (1.0f + expf(-a.out_gate[(size_t)(row0 + qi1) * a.ldg + h]));
+  }
   bf16* o0 = a.out + (size_t)(row0 + qi0) * a.ldo + (size_t)h * hd;
   bf16* o1 = a.out + (size_t)(row0 + qi1) * a.ldo + (size_t)h * hd;
 #pragma unroll
@@ -271,7 +277,8 @@ extern "C" int hb_attention_prefill_bf16(const void* q, int ldq, void* out, int 
                                          const void* vcache, const int* seq_start, const int* seq_pos0,
                                          const int* seq_pages, int pages_stride, int n_seqs, int max_q_len,
                                          int nh, int nkv, int hd, int page_size, float scale, int window, float softcap,
-                                         const float* sink, const float* gate_bias, void* stream) {
+                                         const float* sink, const float* gate_bias, const float* out_gate, int ldg,
+                                         void* stream) {
   HB_REQUIRE(n_seqs > 0 && max_q_len > 0 && nh > 0 && nkv > 0 && hd > 0, "attention_prefill: sizes must be positive");
   HB_REQUIRE(nh % nkv == 0, "attention_prefill: %d query heads are not a multiple of %d key/value heads", nh, nkv);
   HB_REQUIRE(hd % 16 == 0 && hd <= 256, "attention_prefill: head size %d must be a multiple of 16, at most 256", hd);
@@ -291,7 +298,7 @@ extern "C" int hb_attention_prefill_bf16(const void* q, int ldq, void* out, int 
     smem = stages * 2 * AP_TILE * (hd * 2 + 16);
   }
   PrefillArgs a{(const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)kcache, (const bf16*)vcache, seq_start, seq_pos0,
-                seq_pages, pages_stride, nh, nkv, hd, page_size, scale, window, stages, softcap, sink, gate_bias};
+                seq_pages, pages_stride, nh, nkv, hd, page_size, scale, window, stages, softcap, sink, gate_bias, out_gate, ldg};
   dim3 grid(ceil_div(max_q_len, AP_QTILE), nh, n_seqs);
   cudaStream_t s = (cudaStream_t)stream;
   cudaError_t e;

@@ -55,6 +55,8 @@ struct PrefillTcArgs {
   float softcap;         // > 0: score <- softcap * tanh(score * scale / softcap)
   const float* sink;     // [nh] or null: e^{sink} joins the row's sum (the row starts at m = sink, l = 1)
   const float* gate_bias;  // [nh] or null.  Not null: sigmoid weights (see the head of this file)
+  const float* out_gate;   // [tokens, ldg] or null: head h's result of a token is multiplied by sigmoid(out_gate[token * ldg + h])
+  int ldg;
 };
 
 // One unit of work: 128 consecutive queries of two heads (or one) of one key/value head of one sequence.
@@ -451,7 +453,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int ct = c_t + n_tiles - 1;
         if (!mbar_wait(bar(17 + t), ct & 1)) { if (lane == 0) atomicExch(a.error_flag, 36); ok = false; break; }
         tc_fence_after();
-        const float inv = gated ? 1.0f : (l > 0.0f ? 1.0f / l : 0.0f);
+        float inv = gated ? 1.0f : (l > 0.0f ? 1.0f / l : 0.0f);
+        if (a.out_gate != nullptr && valid) inv *= 1.0f / (1.0f + expf(-a.out_gate[(size_t)(it.row0 + qi) * a.ldg + it.h0 + t]));
         bf16* dst = a.out + (size_t)(it.row0 + qi) * a.ldo + (size_t)(it.h0 + t) * HD;
 #pragma unroll
         for (int cc = 0; cc < HD / 32; ++cc) {
@@ -494,8 +497,8 @@ extern "C" int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens
                                             const void* vcache, int n_pages, const int* seq_start, const int* seq_pos0,
                                             const int* seq_pages, int pages_stride, int n_seqs, int max_q_len, int nh,
                                             int nkv, int hd, int page_size, float scale, int window, float softcap,
-                                            const float* sink, const float* gate_bias, int* error_flag, int* work_counter,
-                                            void* stream) {
+                                            const float* sink, const float* gate_bias, const float* out_gate, int ldg,
+                                            int* error_flag, int* work_counter, void* stream) {
   HB_REQUIRE(n_seqs > 0 && max_q_len > 0 && nh > 0 && nkv > 0 && n_tokens > 0 && n_pages > 0, "attention_prefill_tc: sizes must be positive");
   HB_REQUIRE(hd == 64 || hd == 128, "attention_prefill_tc: head size %d is not 64 or 128", hd);
   HB_REQUIRE(nh % nkv == 0, "attention_prefill_tc: %d query heads are not a multiple of %d key/value heads", nh, nkv);
@@ -518,7 +521,7 @@ extern "C" int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens
   if (rc) return rc;
   const int q_tiles = ceil_div(max_q_len, PT_Q);
   PrefillTcArgs a{(bf16*)out, ldo, seq_start, seq_pos0, seq_pages, pages_stride, nh, nkv, page_size,
-                  scale * 1.4426950408889634f, window, error_flag, n_seqs, q_tiles, work_counter, softcap, sink, gate_bias};
+                  scale * 1.4426950408889634f, window, error_flag, n_seqs, q_tiles, work_counter, softcap, sink, gate_bias, out_gate, ldg};
   cudaStream_t s = (cudaStream_t)stream;
   const int pairs = (nh / nkv + 1) / 2;
   const long long items = (long long)q_tiles * n_seqs * nkv * pairs;

@@ -15,6 +15,7 @@
 // as if it were a first key without a value.  The value plane may be the key plane itself.
 // A third option replaces the softmax: with `gate_bias` (a number per query head) the weight of a visible key
 // is sigmoid(s_j + gate_bias[h]), used as it is (nothing is normalised over the keys): o = sum_j w_j v_j.
+// And a fourth: with `out_gate` a head's result is multiplied by sigmoid(out_gate[token, head]) before it is rounded.
 #include "api.h"
 #include "common.cuh"
 
@@ -38,6 +39,8 @@ struct AttnArgs {
   float softcap;
   const float* sink;
   const float* gate_bias;
+  const float* out_gate;   // [n_tokens, ldg] or null: head h's result of token t is multiplied by sigmoid(out_gate[t * ldg + h])
+  int ldg;
 };
 
 template <typename T>
@@ -102,7 +105,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_simt_kernel(AttnArgs
       }
     }
   }
-  const float inv = gated ? 1.0f : (l > 0.0f ? 1.0f / l : 0.0f);
+  float inv = gated ? 1.0f : (l > 0.0f ? 1.0f / l : 0.0f);
+  if (a.out_gate != nullptr) inv *= 1.0f / (1.0f + expf(-a.out_gate[(size_t)t * a.ldg + h]));
   T* op = (T*)a.out + (size_t)t * a.ldo + (size_t)h * a.hd;
 #pragma unroll
   for (int i = 0; i < ATT_MAX_HD / 32; ++i) {
@@ -115,7 +119,7 @@ extern "C" int hb_attention_simt(int dtype, const void* q, int ldq, void* out, i
                                  const void* vcache, const int* tok_seq, const int* tok_pos,
                                  const int* seq_pages, int pages_stride, int n_tokens, int nh, int nkv,
                                  int hd, int page_size, float scale, int window, float softcap, const float* sink,
-                                 const float* gate_bias, void* stream) {
+                                 const float* gate_bias, const float* out_gate, int ldg, void* stream) {
   HB_REQUIRE(n_tokens > 0 && nh > 0 && nkv > 0 && hd > 0 && page_size > 0, "attention: sizes must be positive");
   HB_REQUIRE(nh % nkv == 0, "attention: %d query heads are not a multiple of %d key/value heads", nh, nkv);
   HB_REQUIRE(hd <= ATT_MAX_HD, "attention: head size %d exceeds the supported maximum %d", hd, ATT_MAX_HD);
@@ -123,7 +127,7 @@ extern "C" int hb_attention_simt(int dtype, const void* q, int ldq, void* out, i
   HB_REQUIRE(softcap >= 0.0f, "attention: the cap on the scores must be >= 0 (0: none)");
   HB_REQUIRE(gate_bias == nullptr || sink == nullptr, "attention: sigmoid weights have no sink");
   AttnArgs a{q, ldq, out, ldo, kcache, vcache, tok_seq, tok_pos, seq_pages, pages_stride,
-             n_tokens, nh, nkv, hd, page_size, scale, window, softcap, sink, gate_bias};
+             n_tokens, nh, nkv, hd, page_size, scale, window, softcap, sink, gate_bias, out_gate, ldg};
   const long long blocks = ceil_div_ll((long long)n_tokens * nh, ATT_WARPS);
   HB_REQUIRE(blocks < 2147483647LL, "attention: too many (token, head) pairs");
   if (dtype == HB_F32)

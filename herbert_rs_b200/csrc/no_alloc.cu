@@ -9,7 +9,8 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
                                         const void* vcache, const int* seq_len, const int* seq_pages,
                                         int pages_stride, float* scratch, int n_seqs, int nh, int nkv, int hd,
                                         int page_size, int nsplit, float scale, int window, float softcap,
-                                        const float* sink, const float* gate_bias, void* stream);
+                                        const float* sink, const float* gate_bias, const float* out_gate, int ldg,
+                                        void* stream);
 
 // The partial (m, l, o) results of the key splits.  In host code this name is only a handle for
 // the runtime's symbol calls, never a pointer a kernel could use; its device address is looked up
@@ -42,5 +43,5 @@ extern "C" int hb_attention_decode_bf16_noalloc(const void* q, int ldq, void* ou
   }
   return hb_attention_decode_bf16(q, ldq, out, ldo, kcache, vcache, seq_len, seq_pages, pages_stride,
                                   g_scratch_addr[device], n_seqs, nh, nkv, hd, page_size, nsplit, scale, window, 0.0f, nullptr,
-                                  nullptr, stream);
+                                  nullptr, nullptr, 0, stream);
 }

@@ -15,7 +15,7 @@
 //   hb_rotate_heads_back    y[t, h, :dv] = a head's attention result turned by -p (pair m by -p * fv[m]), compacted
 //                           from heads of hd channels to heads of dv
 //   hb_head_gate            y[t, h, :dv] = a head's attention result times sigmoid(g[t, h]) (one number per token and
-//                           head), compacted likewise
+//                           head; g null: as it is), compacted likewise
 #include "api.h"
 #include "common.cuh"
 
@@ -168,7 +168,7 @@ head_gate_kernel(const T* __restrict__ att, int ld, int hd, const float* __restr
   T* yr = y + (size_t)t * ldy;
   for (int i = threadIdx.x; i < nh * dv; i += blockDim.x) {
     const int h = i / dv, j = i - h * dv;
-    const float g = 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h]));
+    const float g = gate ? 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h])) : 1.0f;
     yr[i] = from_f32<T>(to_f32(ar[(size_t)h * hd + j]) * g);
   }
 }

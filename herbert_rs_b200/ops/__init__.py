@@ -55,19 +55,20 @@ _SIGS = {
     "hb_gemm_stream_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                             ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p],
     "hb_attention_simt": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p],
+                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p,
+                          c_int, c_void_p],
     "hb_attention_decode_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p,
-                                 c_void_p],
+                                 c_void_p, c_int, c_void_p],
     "hb_attention_decode_fused_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
                                        c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_attention_prefill_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p,
-                                  c_void_p],
+                                  c_void_p, c_int, c_void_p],
     "hb_attention_prefill_tc_bf16": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p,
-                                     c_void_p, c_void_p, c_void_p, c_void_p],
+                                     c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
     "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p],
     "hb_gemm_skinny_norm_parts": [c_int, c_int],
     "hb_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -658,9 +659,11 @@ def rotate_heads_back(att, hd, fv, halves, tok_pos, out, num_heads, dv) -> None:
 
 def head_gate(att, hd, gate, out, num_heads, dv) -> None:
     """out[t, h, :dv] = the first dv channels of head h of att (heads of hd channels) times sigmoid(gate[t, h]);
-    gate float [T, num_heads] (rows may be strided)."""
-    _check(att, out.dtype, "att"); _check(gate, torch.float32, "gate")
-    _run("hb_head_gate", dtype_code(out.dtype), att.data_ptr(), att.stride(0), int(hd), gate.data_ptr(), gate.stride(0),
+    gate float [T, num_heads] (rows may be strided), or None: the channels as they are."""
+    _check(att, out.dtype, "att")
+    if gate is not None:
+        _check(gate, torch.float32, "gate")
+    _run("hb_head_gate", dtype_code(out.dtype), att.data_ptr(), att.stride(0), int(hd), _ptr(gate), gate.stride(0) if gate is not None else 0,
          out.data_ptr(), out.stride(0), att.shape[0], int(num_heads), int(dv), _stream())
 
 
@@ -841,18 +844,30 @@ def gemm_simt(a, w, c, epilogue=EPI_STORE) -> None:
 
 
 def attention_simt(q, ldq, out, k_cache, v_cache, tok_seq, tok_pos, seq_pages, num_heads, num_kv_heads,
-                   head_dim, page_size, scale, window, softcap=None, sink=None, gate_bias=None) -> None:
+                   head_dim, page_size, scale, window, softcap=None, sink=None, gate_bias=None, out_gate=None) -> None:
     """Any shape, both precisions.  softcap c: score <- c * tanh(score / c); sink [num_heads] float: exp(sink)
     joins each head's softmax denominator.  v_cache may be k_cache (values that are the keys).  gate_bias
-    [num_heads] float: no softmax, a visible key weighs sigmoid(score + gate_bias[head]) as it is."""
+    [num_heads] float: no softmax, a visible key weighs sigmoid(score + gate_bias[head]) as it is.  out_gate
+    [tokens, num_heads] float (rows may be strided): a head's result is multiplied by sigmoid(out_gate[token, head])."""
     if sink is not None:
         _check(sink, torch.float32, "sink")
     if gate_bias is not None:
         _check(gate_bias, torch.float32, "gate_bias")
+    og, ldg = _out_gate(out_gate, out.shape[0], num_heads)
     _run("hb_attention_simt", dtype_code(out.dtype), q.data_ptr(), int(ldq), out.data_ptr(), out.stride(0),
          k_cache.data_ptr(), v_cache.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_pages.data_ptr(),
          seq_pages.stride(0), out.shape[0], num_heads, num_kv_heads, head_dim, page_size, float(scale),
-         int(window or 0), float(softcap or 0.0), _ptr(sink), _ptr(gate_bias), _stream())
+         int(window or 0), float(softcap or 0.0), _ptr(sink), _ptr(gate_bias), og, ldg, _stream())
+
+
+def _out_gate(out_gate, rows, num_heads):
+    """(pointer, row stride) of a gate per token and head, float [rows, num_heads]; (None, 0) without one."""
+    if out_gate is None:
+        return None, 0
+    _check(out_gate, torch.float32, "out_gate")
+    if tuple(out_gate.shape) != (rows, num_heads):
+        raise BackendError(f"attention: the gate per token and head must be [{rows}, {num_heads}], got {tuple(out_gate.shape)}")
+    return out_gate.data_ptr(), out_gate.stride(0)
 
 
 _argmax_scratch: dict = {}
@@ -1210,7 +1225,7 @@ def decode_splits(n_seqs: int, num_kv_heads: int, max_tiles: int, device=None) -
 
 
 def attention_decode(q, ldq, out, k_cache, v_cache, seq_len, seq_pages, scratch, num_heads, num_kv_heads,
-                     head_dim, page_size, nsplit, scale, window, softcap=None, sink=None, gate_bias=None) -> None:
+                     head_dim, page_size, nsplit, scale, window, softcap=None, sink=None, gate_bias=None, out_gate=None) -> None:
     """One query per sequence (row b of q) over the cache; scratch holds the splits' partial results.
     softcap, sink and gate_bias as in `attention`; the sink joins the denominator where the splits are combined."""
     if sink is not None:
@@ -1224,7 +1239,7 @@ def attention_decode(q, ldq, out, k_cache, v_cache, seq_len, seq_pages, scratch,
     _run("hb_attention_decode_bf16", q.data_ptr(), int(ldq), out.data_ptr(), out.stride(0), k_cache.data_ptr(),
          v_cache.data_ptr(), seq_len.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0), scratch.data_ptr(),
          n, num_heads, num_kv_heads, head_dim, page_size, int(nsplit), float(scale), int(window or 0),
-         float(softcap or 0.0), _ptr(sink), _ptr(gate_bias), _stream())
+         float(softcap or 0.0), _ptr(sink), _ptr(gate_bias), *_out_gate(out_gate, n, num_heads), _stream())
 
 
 _DECODE_COUNTERS = 65536
@@ -1258,7 +1273,7 @@ def attention_decode_fused(qkv, out, k_cache, v_cache, q_weight, k_weight, eps, 
 
 def attention_prefill(q, ldq, out, k_cache, v_cache, seq_start, seq_pos0, seq_pages, n_seqs, max_q_len,
                       num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap=None, sink=None,
-                      gate_bias=None) -> None:
+                      gate_bias=None, out_gate=None) -> None:
     """Causal attention of packed query rows (seq_start marks the sequences) over the cache."""
     _check(out, torch.bfloat16, "out")
     if sink is not None:
@@ -1268,12 +1283,12 @@ def attention_prefill(q, ldq, out, k_cache, v_cache, seq_start, seq_pos0, seq_pa
     _run("hb_attention_prefill_bf16", q.data_ptr(), int(ldq), out.data_ptr(), out.stride(0), k_cache.data_ptr(),
          v_cache.data_ptr(), seq_start.data_ptr(), seq_pos0.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0),
          int(n_seqs), int(max_q_len), num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
-         float(softcap or 0.0), _ptr(sink), _ptr(gate_bias), _stream())
+         float(softcap or 0.0), _ptr(sink), _ptr(gate_bias), *_out_gate(out_gate, out.shape[0], num_heads), _stream())
 
 
 def attention_prefill_tc(q, ldq, out, k_cache, v_cache, seq_start, seq_pos0, seq_pages, n_seqs, max_q_len,
                          num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap=None, sink=None,
-                         gate_bias=None) -> None:
+                         gate_bias=None, out_gate=None) -> None:
     """The same on tcgen05 tensor cores (head sizes 64 and 128): S and O in tensor memory."""
     _check(out, torch.bfloat16, "out")
     if sink is not None:
@@ -1284,7 +1299,8 @@ def attention_prefill_tc(q, ldq, out, k_cache, v_cache, seq_start, seq_pos0, seq
          k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[0], seq_start.data_ptr(), seq_pos0.data_ptr(),
          seq_pages.data_ptr(), seq_pages.stride(0), int(n_seqs), int(max_q_len), num_heads, num_kv_heads, head_dim,
          page_size, float(scale), int(window or 0), float(softcap or 0.0), _ptr(sink), _ptr(gate_bias),
-         _error_flag(out.device).data_ptr(), _work_counter(out.device).data_ptr(), _stream())
+         *_out_gate(out_gate, out.shape[0], num_heads), _error_flag(out.device).data_ptr(), _work_counter(out.device).data_ptr(),
+         _stream())
 
 
 _work_counters: dict = {}
@@ -1314,32 +1330,35 @@ def _decode_kernel_ok(out, num_heads, num_kv_heads, head_dim, page_size) -> bool
 
 
 def attention(q, ldq, out, k_cache, v_cache, batch, num_heads, num_kv_heads, head_dim, page_size,
-              scale, window, seq_pages, scratch=None, softcap=None, sink=None, gate_bias=None) -> None:
+              scale, window, seq_pages, scratch=None, softcap=None, sink=None, gate_bias=None, out_gate=None) -> None:
     """Attention of every token of the step over its sequence's cached keys and values.
 
     bfloat16 steps of one token per sequence take the split-key tensor-core kernel, other bfloat16
     steps the flash kernel; head sizes or pages those cannot serve, and the float32 path, take
     the any-shape kernel.  Every kernel takes a cap on the scores (softcap c: s <- c * tanh(s / c)) and a sink
     (a float per query head whose exponential joins the softmax's denominator); v_cache may be k_cache.  With
-    `gate_bias` (a float per query head) there is no softmax: a visible key weighs sigmoid(score + gate_bias[head])."""
+    `gate_bias` (a float per query head) there is no softmax: a visible key weighs sigmoid(score + gate_bias[head]).  With
+    `out_gate` (float [tokens, num_heads]) a head's result is multiplied by sigmoid(out_gate[token, head]) before it is rounded."""
     if options.attention == "simt":
         attention_simt(q, ldq, out, k_cache, v_cache, batch.tok_seq, batch.tok_pos, seq_pages, num_heads,
-                       num_kv_heads, head_dim, page_size, scale, window, softcap, sink, gate_bias)
+                       num_kv_heads, head_dim, page_size, scale, window, softcap, sink, gate_bias, out_gate)
         return
     if batch.is_decode and scratch is not None and _decode_kernel_ok(out, num_heads, num_kv_heads, head_dim, page_size):
         tiles = seq_pages.shape[1] * (page_size // 64)
         nsplit = decode_splits(batch.n_seqs, num_kv_heads, tiles)
         buf = scratch((attention_decode_scratch_floats(batch.n_seqs, num_heads, head_dim, nsplit),), torch.float32)
         attention_decode(q, ldq, out, k_cache, v_cache, batch.seq_len, seq_pages, buf, num_heads, num_kv_heads,
-                         head_dim, page_size, nsplit, scale, window, softcap, sink, gate_bias)
+                         head_dim, page_size, nsplit, scale, window, softcap, sink, gate_bias, out_gate)
         return
     if _prefill_tc_ok(q, ldq, out, head_dim, page_size):
         attention_prefill_tc(q, ldq, out, k_cache, v_cache, batch.seq_start, batch.seq_pos0, seq_pages, batch.n_seqs,
-                             batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap, sink, gate_bias)
+                             batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap, sink, gate_bias,
+                             out_gate)
         return
     if _prefill_kernel_ok(out, head_dim, page_size):
         attention_prefill(q, ldq, out, k_cache, v_cache, batch.seq_start, batch.seq_pos0, seq_pages, batch.n_seqs,
-                          batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap, sink, gate_bias)
+                          batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap, sink, gate_bias,
+                          out_gate)
         return
     attention_simt(q, ldq, out, k_cache, v_cache, batch.tok_seq, batch.tok_pos, seq_pages, num_heads,
-                   num_kv_heads, head_dim, page_size, scale, window, softcap, sink, gate_bias)
+                   num_kv_heads, head_dim, page_size, scale, window, softcap, sink, gate_bias, out_gate)

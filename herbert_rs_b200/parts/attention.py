@@ -159,16 +159,17 @@ class AttentionMixer(Mixer):
                              batch, pages, q, cache.k, cache.v, self.nh, self.nkv, self.dk, self.dv, self.hd,
                              cache.page_size, write_cache=cache.writes_kv and not self.reads_kv)
         att = ws.take((T, self.nh * self.hd), h.dtype)
+        # the gate per token and head multiplies a head's float result inside the attention kernel, before it is rounded
         ops.attention(q, q.stride(0), att, cache.k, cache.v, batch, self.nh, self.nkv, self.hd, cache.page_size, s.scale,
-                      s.window, pages, scratch=ws.take, gate_bias=self.key_bias)
-        y, hd = att, self.hd
-        if fv is not None or (self.hd != self.dv and not s.head_gate):
-            y, hd = ws.take((T, self.nh * self.dv), h.dtype), self.dv
+                      s.window, pages, scratch=ws.take, gate_bias=self.key_bias,
+                      out_gate=proj[:, self.qkv_dim:] if s.head_gate else None)
+        y = att
+        if fv is not None:
+            y = ws.take((T, self.nh * self.dv), h.dtype)
             ops.rotate_heads_back(att, self.hd, fv, halves, batch.tok_pos, y, self.nh, self.dv)
-        if s.head_gate:
-            gated = ws.take((T, self.nh * self.dv), h.dtype)
-            ops.head_gate(y, hd, proj[:, self.qkv_dim:], gated, self.nh, self.dv)
-            y = gated
+        elif self.hd != self.dv:          # heads of the cache's width -> heads of the values' width
+            y = ws.take((T, self.nh * self.dv), h.dtype)
+            ops.head_gate(att, self.hd, None, y, self.nh, self.dv)
         ops.gemm(y, self.wo, residual, ops.EPI_RESIDUAL if accumulate else ops.EPI_STORE_F32, scratch=ws.take)
 
     def param_specs(self):

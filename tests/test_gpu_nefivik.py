@@ -127,6 +127,8 @@ def test_token_gate_and_head_gate(dtype):
     ops.head_gate(att.to(DEV), hd, gate.to(DEV)[:, 1:1 + H], out, H, dv)
     ref = att.double().view(T, H, hd)[:, :, :dv] * P.sigmoid(gate.double()[:, 1:1 + H])[:, :, None]
     assert_close(to_np(out), ref.reshape(T, H * dv).numpy(), dtype, "head gate")
+    ops.head_gate(att.to(DEV), hd, None, out, H, dv)
+    assert np.array_equal(to_np(out), att.double().view(T, H, hd)[:, :, :dv].reshape(T, H * dv).numpy())
 
 
 def _delta_inputs(g, T, H, n, nv, rank, extreme=False):
@@ -242,6 +244,9 @@ def test_sigmoid_weights_in_every_attention_kernel(H, G, dk, dv, window):
         if 0 <= j < T:
             k[0, j] = q[last, 0] * 3.0
     ref = P.sigmoid_attention(q.double(), k.double().transpose(0, 1), v.double().transpose(0, 1), scale, window, bias.double())
+    gate = torch.randn(T, H + 3, generator=g) * 2.0          # a gate per token and head, in rows with a stride of their own
+    ref_plain, ref = ref, ref * P.sigmoid(gate.double()[:, 1:1 + H])[:, :, None]
+    gd = gate.to(DEV)
     rows = list(range(T - 70, T))
     for dtype in DTYPES:
         kc, vc, pages = _paged(k, v, hd, page, order, dtype)
@@ -256,23 +261,29 @@ def test_sigmoid_weights_in_every_attention_kernel(H, G, dk, dv, window):
                 batch = step_of([70], [0], [T - 70])
                 out = torch.empty(70, H * hd, dtype=td_of(dtype), device=DEV)
                 ops.attention(qd[T - 70:], H * hd, out, kc, vc, batch, H, G, hd, page, scale, window, pages,
-                              scratch=lambda shape, dt: torch.empty(shape, dtype=dt, device=DEV), gate_bias=bias.to(DEV))
+                              scratch=lambda shape, dt: torch.empty(shape, dtype=dt, device=DEV), gate_bias=bias.to(DEV),
+                              out_gate=gd[T - 70:, 1:1 + H])
                 got = to_np(out).reshape(70, H, hd)[:, :, :dv]
                 bound = 2e-5 * max(1.0, float(ref.abs().max())) if dtype == "float32" else 1.5e-2 * float(ref[rows].abs().amax())
                 assert np.abs(got - ref[rows].numpy()).max() < bound, (dtype, kern, "portion")
                 batch = step_of([1], [0], [T - 1])
                 out = torch.empty(1, H * hd, dtype=td_of(dtype), device=DEV)
                 ops.attention(qd[T - 1:], H * hd, out, kc, vc, batch, H, G, hd, page, scale, window, pages,
-                              scratch=lambda shape, dt: torch.empty(shape, dtype=dt, device=DEV), gate_bias=bias.to(DEV))
+                              scratch=lambda shape, dt: torch.empty(shape, dtype=dt, device=DEV), gate_bias=bias.to(DEV),
+                              out_gate=gd[T - 1:, 1:1 + H])
                 got = to_np(out).reshape(1, H, hd)[:, :, :dv]
                 assert np.abs(got - ref[[last]].numpy()).max() < bound, (dtype, kern, "alone")
+                ops.attention(qd[T - 1:], H * hd, out, kc, vc, batch, H, G, hd, page, scale, window, pages,
+                              scratch=lambda shape, dt: torch.empty(shape, dtype=dt, device=DEV), gate_bias=bias.to(DEV))
+                got = to_np(out).reshape(1, H, hd)[:, :, :dv]
+                assert np.abs(got - ref_plain[[last]].numpy()).max() < bound, (dtype, kern, "alone, no gate")
                 ops.check_kernel_errors()
             finally:
                 ops.options.attention, ops.options.prefill_attention = "auto", "tcgen05"
     if window and 1 < window < T:
         # the window shows: one key more moves the last row far beyond any bound
         a = P.sigmoid_attention(q.double(), k.double().transpose(0, 1), v.double().transpose(0, 1), scale, window + 1, bias.double())
-        assert (a[last, 0] - ref[last, 0]).abs().max() > 0.3
+        assert (a[last, 0] - ref_plain[last, 0]).abs().max() > 0.3
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
