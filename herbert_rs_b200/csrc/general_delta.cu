@@ -151,6 +151,7 @@ struct GdScanArgs {
   const int* seq_start;
   float* out; int ldo;
   int H, dk, dv, R;
+  int chunk;                    // tokens per stage: GD_CHUNK, fewer where a head's key channels are many
 };
 
 template <int RPT>
@@ -158,7 +159,8 @@ __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(GdScanAr
   extern __shared__ __align__(16) float sh[];
   __shared__ float outs[GD_CHUNK * GD_THREADS];                   // [GD_CHUNK][cols]: a chunk's read-outs
   const int R = a.R, DKP = R * RPT, cols = GD_THREADS / R;
-  const int stage_floats = GD_CHUNK * (5 * DKP + cols);
+  const int CH = a.chunk;
+  const int stage_floats = CH * (5 * DKP + cols);
   pdl_wait();
   pdl_launch();
   const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
@@ -181,8 +183,8 @@ __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(GdScanAr
 
   auto stage = [&](int buf, int c0) {
     float* ks = sh + buf * stage_floats;                          // [GD_CHUNK][5][DKP]
-    float* vs = ks + GD_CHUNK * 5 * DKP;                          // [GD_CHUNK][cols]
-    const int n = t1 - c0 < GD_CHUNK ? t1 - c0 : GD_CHUNK;
+    float* vs = ks + CH * 5 * DKP;                                // [chunk][cols]
+    const int n = t1 - c0 < CH ? t1 - c0 : CH;
     if (wide) {
       const int per = a.dk >> 2;
       for (int i = tid; i < n * 5 * per; i += GD_THREADS) {
@@ -204,17 +206,17 @@ __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(GdScanAr
 
   if (t0 < t1) stage(0, t0);
   int buf = 0;
-  for (int c0 = t0; c0 < t1; c0 += GD_CHUNK, buf ^= 1) {
-    const int n = t1 - c0 < GD_CHUNK ? t1 - c0 : GD_CHUNK;
-    if (c0 + GD_CHUNK < t1) {
-      stage(buf ^ 1, c0 + GD_CHUNK);
+  for (int c0 = t0; c0 < t1; c0 += CH, buf ^= 1) {
+    const int n = t1 - c0 < CH ? t1 - c0 : CH;
+    if (c0 + CH < t1) {
+      stage(buf ^ 1, c0 + CH);
       asm volatile("cp.async.wait_group 1;");
     } else {
       asm volatile("cp.async.wait_group 0;");
     }
     __syncthreads();
     const float* ks = sh + buf * stage_floats;
-    const float* vs = ks + GD_CHUNK * 5 * DKP;
+    const float* vs = ks + CH * 5 * DKP;
     // Only `seen` of one token stands between it and the next: the read-out's sum and its shuffles belong to no chain, so
     // the loop is unrolled for them to run beside the next token's first sum; the results leave through an array of their
     // own in shared memory (a store into global memory in the loop would keep the next tokens' loads behind it).
@@ -281,9 +283,11 @@ extern "C" int hb_general_delta_scan(const float* prep, const float* v, int ldv,
   rpt = rpt <= 4 ? 4 : rpt <= 8 ? 8 : rpt <= 16 ? 16 : 32;
   const int cols = GD_THREADS / R;
   HB_REQUIRE(heads <= 65535 && ceil_div(dv, cols) <= 65535, "general_delta_scan: too many heads or value channels");
-  const size_t smem = (size_t)2 * GD_CHUNK * (5 * R * rpt + cols) * sizeof(float);
+  int chunk = GD_CHUNK;
+  while (chunk > 2 && (size_t)2 * chunk * (5 * R * rpt + cols) * sizeof(float) > 160 * 1024) chunk >>= 1;
+  const size_t smem = (size_t)2 * chunk * (5 * R * rpt + cols) * sizeof(float);
   HB_REQUIRE(smem <= 192 * 1024, "general_delta_scan: %d key channels per head need %zu bytes of shared memory, more than a CTA has", dk, smem);
-  GdScanArgs a{prep, v, ldv, state, seq_slot, seq_start, out, ldo, heads, dk, dv, R};
+  GdScanArgs a{prep, v, ldv, state, seq_slot, seq_start, out, ldo, heads, dk, dv, R, chunk};
   dim3 grid(n_seqs, heads, ceil_div(dv, cols));
   cudaStream_t s = (cudaStream_t)stream;
 #define GD_GO(RPT)                                                                                                         \

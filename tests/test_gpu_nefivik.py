@@ -156,7 +156,7 @@ def _delta_plain(rows, w2, w0, a0, T, H, n, nv, rank):
 
 
 @pytest.mark.parametrize("wdtype", DTYPES)
-@pytest.mark.parametrize("H,n,nv,rank", [(2, 32, 32, 12), (2, 64, 64, 6), (3, 24, 40, 5), (1, 130, 6, 3), (2, 256, 128, 8), (6, 7, 5, 1)])
+@pytest.mark.parametrize("H,n,nv,rank", [(2, 32, 32, 12), (2, 64, 64, 6), (3, 24, 40, 5), (1, 130, 6, 3), (2, 256, 128, 8), (6, 7, 5, 1), (1, 520, 24, 4)])
 def test_generalised_delta_rule_in_steps_of_any_size(H, n, nv, rank, wdtype):
     """Three sequences in slots out of order, fed in steps of 1, 2, 17 and 33 tokens and more: every step continues the
     recurrence from the slot's state; decays near 0 and 1, removal rates of 0 and 1, a key of zeros."""
